@@ -84,6 +84,8 @@ def resolve_architecture(config: Mapping[str, Any]) -> ArchitectureEntry:
     model_type = str(config.get("model_type", "") or "").strip().lower()
     by_type = _BY_MODEL_TYPE.get(model_type)
     architectures = [str(value) for value in (config.get("architectures") or ())]
+    if isinstance(config.get("architecture"), str):       # (some checkpoints name one design under the singular key)
+        architectures.append(config["architecture"])
     by_arch = {
         _BY_ARCHITECTURE[key].name: _BY_ARCHITECTURE[key]
         for value in architectures
@@ -115,4 +117,4 @@ def _ensure_builtin() -> None:
     if _BUILTIN_LOADED:
         return
     _BUILTIN_LOADED = True
-    from torchinferno_b200.models import llama  # noqa: F401
+    from torchinferno_b200.models import llama, zipedra  # noqa: F401

@@ -25,6 +25,9 @@ struct Blas {
   cublasStatus_t (*gemm_ex)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*, const void*,
                             cudaDataType, int, const void*, cudaDataType, int, const void*, void*, cudaDataType, int,
                             cublasComputeType_t, cublasGemmAlgo_t) = nullptr;
+  cublasStatus_t (*gemm_batched)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*, const void*,
+                                 cudaDataType, int, long long, const void*, cudaDataType, int, long long, const void*, void*,
+                                 cudaDataType, int, long long, int, cublasComputeType_t, cublasGemmAlgo_t) = nullptr;
   bool loaded = false;
   static constexpr int kMaxDevices = 64;
   cublasHandle_t handle[kMaxDevices] = {nullptr};
@@ -48,7 +51,8 @@ static int load_blas() {
   b.set_stream = (decltype(b.set_stream))dlsym(lib, "cublasSetStream_v2");
   b.set_workspace = (decltype(b.set_workspace))dlsym(lib, "cublasSetWorkspace_v2");
   b.gemm_ex = (decltype(b.gemm_ex))dlsym(lib, "cublasGemmEx");
-  if (!b.create || !b.set_stream || !b.set_workspace || !b.gemm_ex) return TIB_E_ARG;
+  b.gemm_batched = (decltype(b.gemm_batched))dlsym(lib, "cublasGemmStridedBatchedEx");
+  if (!b.create || !b.set_stream || !b.set_workspace || !b.gemm_ex || !b.gemm_batched) return TIB_E_ARG;
   b.loaded = true;
   return TIB_OK;
 }
@@ -73,6 +77,27 @@ int blas_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K,
   st = b.gemm_ex(h, w_kn ? CUBLAS_OP_N : CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, (int)ldw, x, CUDA_R_16BF,
                  (int)ldx, &beta, out, out_dtype == TIB_F32 ? CUDA_R_32F : CUDA_R_16BF, (int)ldo, CUBLAS_COMPUTE_32F,
                  CUBLAS_GEMM_DEFAULT_TENSOR_OP);
+  return st == CUBLAS_STATUS_SUCCESS ? TIB_OK : kBlasError + (int)st;
+}
+
+// The same product for `batch` operand triples that lie at fixed strides (elements) from one another: one weight
+// per head, say, applied to that head's slice of every row.
+int blas_gemm_bf16_batched(const void* x, const void* w, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo,
+                           int64_t sx, int64_t sw, int64_t so, int batch, int w_kn, int out_dtype, cudaStream_t stream) {
+  Blas& b = blas();
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= Blas::kMaxDevices || !b.loaded || !b.handle[device]) return TIB_E_ARG;
+  cublasHandle_t h = b.handle[device];
+  cublasStatus_t st = b.set_stream(h, stream);
+  if (st != CUBLAS_STATUS_SUCCESS) return kBlasError + (int)st;
+  st = b.set_workspace(h, b.workspace[device], b.workspace_bytes[device]);
+  if (st != CUBLAS_STATUS_SUCCESS) return kBlasError + (int)st;
+  const float alpha = 1.f, beta = 0.f;
+  st = b.gemm_batched(h, w_kn ? CUBLAS_OP_N : CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, (int)ldw, (long long)sw, x,
+                      CUDA_R_16BF, (int)ldx, (long long)sx, &beta, out, out_dtype == TIB_F32 ? CUDA_R_32F : CUDA_R_16BF, (int)ldo,
+                      (long long)so, batch, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
   return st == CUBLAS_STATUS_SUCCESS ? TIB_OK : kBlasError + (int)st;
 }
 
@@ -109,4 +134,15 @@ TIB_API int tib_blas_gemm(const void* x, const void* w, void* out, int M, int N,
   if (!x || !w || !out || M < 0 || N < 0 || K < 1) return TIB_E_ARG;
   if (out_dtype != TIB_BF16 && out_dtype != TIB_F32) return TIB_E_DTYPE;
   return blas_gemm_bf16(x, w, out, M, N, K, ldx, ldw, ldo, w_kn, out_dtype, stream);
+}
+
+// `batch` products out_b[M, N] = x_b[M, K] . w_b^T whose operands lie sx, sw, so elements apart (bf16 operands, out bf16 or
+// fp32); row strides and layouts as in tib_blas_gemm.
+TIB_API int tib_blas_gemm_batched(const void* x, const void* w, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
+                                  int64_t ldo, int64_t sx, int64_t sw, int64_t so, int batch, int w_kn, int out_dtype,
+                                  cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return TIB_OK;
+  if (!x || !w || !out || M < 0 || N < 0 || K < 1 || batch < 0) return TIB_E_ARG;
+  if (out_dtype != TIB_BF16 && out_dtype != TIB_F32) return TIB_E_DTYPE;
+  return blas_gemm_bf16_batched(x, w, out, M, N, K, ldx, ldw, ldo, sx, sw, so, batch, w_kn, out_dtype, stream);
 }

@@ -1,0 +1,145 @@
+// Linear attention with a fixed decay per head over per-request state:
+//     S_t = lambda * S_(t-1) + k_t v_t^T        (S: [key_dim, value_dim], fp32, one per request, layer call and head)
+//     o_t = S_t^T q_t
+// for the tokens of a ragged batch: portions of prompts and single decoded tokens alike.  An optional
+// activation (silu) is applied to q, k and v as they are read, in fp32.
+//
+// One block owns one (request entry, head).  It keeps S in shared memory and walks the entry's tokens in
+// chunks of up to C: within a chunk of n tokens
+//     A[i][j] = (q_i . k_j) lambda^(i-j)                                    j <= i
+//     o_i     = lambda^(i+1) S^T q_i + sum_(j<=i) A[i][j] v_j
+//     S      <- lambda^n S + sum_j lambda^(n-1-j) k_j v_j^T
+// which is the recurrence written out.  Scores, decay powers, state and sums are fp32; the powers
+// lambda^0 .. lambda^C come from the host as a table (made in double precision).  A single token is a chunk
+// of one.  State is read from and written back to the request's slot; a new request's slot is zero.
+#include "common.cuh"
+
+namespace tib {
+
+struct LinAttnArgs {
+  const int* q_start;     // [n_entries + 1]
+  const int* slots;       // [n_entries]
+  const float* powers;    // [heads, chunk + 1]
+  float* state;           // [slots, heads, key_dim, value_dim]
+  float* out;             // [tokens, heads * value_dim]
+  int64_t ldq, ldk, ldv;  // row strides of q, k, v (elements)
+  int heads, key_dim, value_dim, chunk, activation;
+};
+
+__device__ __forceinline__ float lin_act(float z, int activation) { return activation ? z / (1.f + expf(-z)) : z; }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, LinAttnArgs a) {
+  extern __shared__ float smem[];
+  const int D = a.key_dim, V = a.value_dim, C = a.chunk, DP = D + 1;
+  float* S = smem;                 // [D][V]
+  float* qs = S + D * V;           // [C][DP]
+  float* ks = qs + C * DP;         // [C][DP]
+  float* vs = ks + C * DP;         // [C][V]
+  float* A = vs + C * V;           // [C][C]
+  float* pw = A + C * C;           // [C + 1]
+  const int head = blockIdx.x, entry = blockIdx.y;
+  pdl_wait();
+  pdl_trigger();
+  const int row0 = a.q_start[entry], len = a.q_start[entry + 1] - row0;
+  if (len <= 0) return;
+  float* state = a.state + ((size_t)a.slots[entry] * a.heads + head) * D * V;
+  for (int e = threadIdx.x; e < D * V; e += blockDim.x) S[e] = state[e];
+  for (int e = threadIdx.x; e <= C; e += blockDim.x) pw[e] = a.powers[head * (C + 1) + e];
+
+  for (int t0 = 0; t0 < len; t0 += C) {
+    const int n = min(C, len - t0);
+    __syncthreads();               // the chunk before is done with qs, ks, vs, A (and S, pw are loaded)
+    for (int e = threadIdx.x; e < n * D; e += blockDim.x) {
+      const int i = e / D, d = e - i * D;
+      const size_t row = row0 + t0 + i;
+      qs[i * DP + d] = lin_act(to_f32(q[row * a.ldq + head * D + d]), a.activation);
+      ks[i * DP + d] = lin_act(to_f32(k[row * a.ldk + head * D + d]), a.activation);
+    }
+    for (int e = threadIdx.x; e < n * V; e += blockDim.x) {
+      const int i = e / V, c = e - i * V;
+      vs[i * V + c] = lin_act(to_f32(v[(size_t)(row0 + t0 + i) * a.ldv + head * V + c]), a.activation);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * n; e += blockDim.x) {
+      const int i = e / n, j = e - i * n;
+      float s = 0.f;
+      if (j <= i) {
+        for (int d = 0; d < D; ++d) s = fmaf(qs[i * DP + d], ks[j * DP + d], s);
+        s *= pw[i - j];
+      }
+      A[i * C + j] = s;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * V; e += blockDim.x) {
+      const int i = e / V, c = e - i * V;
+      float carried = 0.f, inside = 0.f;
+      for (int d = 0; d < D; ++d) carried = fmaf(qs[i * DP + d], S[d * V + c], carried);
+      for (int j = 0; j <= i; ++j) inside = fmaf(A[i * C + j], vs[j * V + c], inside);
+      a.out[(size_t)(row0 + t0 + i) * a.heads * V + head * V + c] = fmaf(pw[i + 1], carried, inside);
+    }
+    __syncthreads();               // every o of the chunk has read the old S
+    for (int e = threadIdx.x; e < D * V; e += blockDim.x) {
+      const int d = e / V, c = e - d * V;
+      float add = 0.f;
+      for (int j = 0; j < n; ++j) add = fmaf(pw[n - 1 - j] * ks[j * DP + d], vs[j * V + c], add);
+      S[e] = fmaf(pw[n], S[e], add);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < D * V; e += blockDim.x) state[e] = S[e];
+}
+
+static inline size_t lin_attn_smem(int D, int V, int C) {
+  return sizeof(float) * ((size_t)D * V + 2 * (size_t)C * (D + 1) + (size_t)C * V + (size_t)C * C + C + 1);
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// The largest chunk (32, 16, 8, 4, 2 or 1 tokens) whose working set fits an SM's shared memory; 0 if none does.
+TIB_API int tib_linear_attention_chunk(int key_dim, int value_dim) {
+  for (int c = 32; c >= 1; c >>= 1)
+    if (lin_attn_smem(key_dim, value_dim, c) <= 227 * 1024) return c;
+  return 0;
+}
+
+// q, k: [tokens, >= heads * key_dim] and v: [tokens, >= heads * value_dim] with row strides ldq, ldk, ldv (they may be
+// slices of one wider row); out: [tokens, heads * value_dim] fp32; state: [slots, heads, key_dim, value_dim] fp32;
+// powers: [heads, chunk + 1] fp32, powers[h][m] = lambda_h^m; activation: 0 none, 1 silu on q, k and v.
+TIB_API int tib_linear_attention(const void* q, const void* k, const void* v, int64_t ldq, int64_t ldk, int64_t ldv,
+                                 float* out, float* state, const float* powers, const int* q_start, const int* slots,
+                                 int n_entries, int heads, int key_dim, int value_dim, int chunk, int activation, int dtype,
+                                 cudaStream_t stream) {
+  if (n_entries == 0) return TIB_OK;
+  if (!q || !k || !v || !out || !state || !powers || !q_start || !slots) return TIB_E_ARG;
+  if (heads < 1 || key_dim < 1 || value_dim < 1 || chunk < 1 || chunk > 32 || n_entries > 65535) return TIB_E_SIZE;
+  const size_t smem = lin_attn_smem(key_dim, value_dim, chunk);
+  if (smem > 227 * 1024) return TIB_E_SMEM;
+  LinAttnArgs a;
+  a.q_start = q_start; a.slots = slots; a.powers = powers; a.state = state; a.out = out;
+  a.ldq = ldq; a.ldk = ldk; a.ldv = ldv;
+  a.heads = heads; a.key_dim = key_dim; a.value_dim = value_dim; a.chunk = chunk; a.activation = activation;
+  dim3 grid(heads, n_entries);
+  if (dtype == TIB_F32) {
+    auto kern = linear_attention_kernel<float>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    TIB_LAUNCH_DEPENDENT(kern, grid, 256, smem, stream, (const float*)q, (const float*)k, (const float*)v, a);
+  } else if (dtype == TIB_BF16) {
+    auto kern = linear_attention_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    TIB_LAUNCH_DEPENDENT(kern, grid, 256, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
+                         (const __nv_bfloat16*)v, a);
+  } else {
+    return TIB_E_DTYPE;
+  }
+  return TIB_OK;
+}

@@ -1,0 +1,255 @@
+// Routed feed-forward (mixture of experts): routing, grouping of (token, choice) pairs by expert, the experts'
+// two products over the grouped rows, and the weighted sum back per token.  Nothing here returns to the host:
+// every count and offset stays on the device and grids are sized for the worst case, so a step can be captured.
+//
+//   moe_route    from fp32 router logits [tokens, ld]: softmax over the experts (or sigmoid), the `top` largest
+//                scores (lowest index first among equals), their weights = score / (sum of the chosen + norm_eps)
+//                (or the bare scores), all fp32
+//   moe_group    counting sort of the tokens * top pairs by expert: offsets [experts + 1], order[sorted] = pair,
+//                place[pair] = sorted index.  The order inside an expert may differ from run to run; every row
+//                of a product is computed by itself, so no value depends on it
+//   moe_expert_product   y[s] = act(x[src(s)] . W_e^T) for the sorted rows s of expert e; W: [experts, n, k];
+//                fp32 FMAs in fixed k order (operands float or bf16 in memory); act: none, relu^2, silu
+//   moe_combine  out[t] = sum_k weight[t, k] * y[place[t * top + k]]  (+ sigmoid(gate[t]) * shared[t])
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace tib {
+
+// ------------------------------------------------------------------- route
+__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int experts, int top, int sigmoid_scores,
+                                 int normalize, float norm_eps, int* __restrict__ ids, float* __restrict__ weights, int tokens) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const float* z = logits + (size_t)t * ld;
+  float mx = -CUDART_INF_F;
+  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < experts; e += 32) sum += expf(z[e] - mx);
+  sum = warp_sum(sum);
+  float chosen_sum = 0.f;
+  unsigned long long taken_lo = 0ull;    // lane-local mask over this lane's experts (e = lane + 32 * i, i < 64)
+  for (int k = 0; k < top; ++k) {
+    float best = -CUDART_INF_F;
+    int best_e = 0x7fffffff;
+    for (int e = lane, i = 0; e < experts; e += 32, ++i) {
+      if ((taken_lo >> i) & 1ull) continue;
+      const float s = sigmoid_scores ? 1.f / (1.f + expf(-z[e])) : expf(z[e] - mx) / sum;
+      if (s > best) { best = s; best_e = e; }     // (rising e: the lowest index wins among equals)
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if ((best_e & 31) == lane && best_e < experts) taken_lo |= 1ull << (best_e >> 5);
+    chosen_sum += best;
+    if (lane == 0) { ids[(size_t)t * top + k] = best_e; weights[(size_t)t * top + k] = best; }
+  }
+  __syncwarp();
+  if (normalize && lane < top) weights[(size_t)t * top + lane] /= (chosen_sum + norm_eps);
+  if (normalize) for (int k = lane + 32; k < top; k += 32) weights[(size_t)t * top + k] /= (chosen_sum + norm_eps);
+}
+
+// ------------------------------------------------------------------- group
+// One block.  counts in shared memory (experts <= 1024), exclusive scan by one warp, then placement with atomics.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ offsets, int* __restrict__ order,
+                 int* __restrict__ place) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int count[1024];
+  __shared__ int cursor[1024];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) { offsets[e] = run; cursor[e] = run; run += count[e]; }
+    offsets[experts] = run;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < experts) {
+      const int s = atomicAdd(&cursor[e], 1);
+      order[s] = p;
+      place[p] = s;
+    } else {
+      place[p] = -1;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- products
+constexpr int GM = 64, GN = 64, GK = 16;
+enum MoeAct : int { MOE_ACT_NONE = 0, MOE_ACT_RELU2 = 1, MOE_ACT_SILU = 2 };
+
+// Row tile `blockIdx.y` counts tiles of GM sorted rows expert by expert; it finds its expert by walking offsets.
+// x_by_pair: source row of sorted row s is order[s] / top (the token), else s itself (rows already sorted).
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+moe_expert_product_kernel(const TX* __restrict__ x, int64_t ldx, const TW* __restrict__ w, TO* __restrict__ y, int64_t ldy,
+                          const int* __restrict__ offsets, const int* __restrict__ order, int experts, int top,
+                          int x_by_pair, int N, int K, int act) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float xs[GK][GM + 4];
+  __shared__ float ws[GK][GN + 4];
+  __shared__ int src_row[GM];
+  __shared__ int tile_info[3];     // expert, first sorted row, rows
+  if (threadIdx.x == 0) {
+    int tile = blockIdx.y, e = 0, found = -1, first = 0, rows = 0;
+    for (; e < experts; ++e) {
+      const int lo = offsets[e], n = offsets[e + 1] - lo;
+      const int tiles = (n + GM - 1) / GM;
+      if (tile < tiles) { found = e; first = lo + tile * GM; rows = min(GM, n - tile * GM); break; }
+      tile -= tiles;
+    }
+    tile_info[0] = found; tile_info[1] = first; tile_info[2] = rows;
+  }
+  __syncthreads();
+  const int expert = tile_info[0], first = tile_info[1], rows = tile_info[2];
+  if (expert < 0) return;
+  const int tid = threadIdx.x;
+  if (tid < GM) src_row[tid] = tid < rows ? (x_by_pair ? order[first + tid] / top : first + tid) : -1;
+  __syncthreads();
+  const TW* we = w + (size_t)expert * N * K;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int n0 = blockIdx.x * GN;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += GK) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int e = tid + it * 256;
+      const int r = e >> 4, c = e & 15;
+      const int gk = k0 + c, gn = n0 + r;
+      const int sr = src_row[r];
+      xs[c][r] = (sr >= 0 && gk < K) ? to_f32(x[(size_t)sr * ldx + gk]) : 0.f;
+      ws[c][r] = (gn < N && gk < K) ? to_f32(we[(size_t)gn * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (act == MOE_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+      else if (act == MOE_ACT_SILU) v = v / (1.f + expf(-v));
+      y[(size_t)(first + r) * ldy + gn] = from_f32<TO>(v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------- combine
+template <typename TS, typename TO>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
+                                   int top, const TS* __restrict__ shared, const float* __restrict__ gate, int64_t ld_gate,
+                                   TO* __restrict__ out, int width) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t t = blockIdx.x;
+  const float g = (shared && gate) ? 1.f / (1.f + expf(-gate[t * ld_gate])) : 1.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int s = place[t * top + k];
+      if (s >= 0) v = fmaf(weights[t * top + k], y[(size_t)s * width + c], v);
+    }
+    if (shared) v = fmaf(g, to_f32(shared[t * width + c]), v);
+    out[t * width + c] = from_f32<TO>(v);
+  }
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+TIB_API int tib_moe_route(const float* logits, int64_t ld, int tokens, int experts, int top, int sigmoid_scores, int normalize,
+                          float norm_eps, int* ids, float* weights, cudaStream_t stream) {
+  if (tokens == 0) return TIB_OK;
+  if (!logits || !ids || !weights) return TIB_E_ARG;
+  if (experts < 1 || experts > 2048 || top < 1 || top > experts) return TIB_E_SIZE;
+  TIB_LAUNCH_DEPENDENT(moe_route_kernel, ceil_div(tokens, 4), 128, 0, stream, logits, ld, experts, top, sigmoid_scores, normalize,
+                       norm_eps, ids, weights, tokens);
+  return TIB_OK;
+}
+
+TIB_API int tib_moe_group(const int* ids, int pairs, int experts, int* offsets, int* order, int* place, cudaStream_t stream) {
+  if (!ids || !offsets || !order || !place) return TIB_E_ARG;
+  if (experts < 1 || experts > 1024 || pairs < 0) return TIB_E_SIZE;
+  TIB_LAUNCH_DEPENDENT(moe_group_kernel, 1, 1024, 0, stream, ids, pairs, experts, offsets, order, place);
+  return TIB_OK;
+}
+
+// x: rows of K (row stride ldx) in x_dtype; w: [experts, N, K] in w_dtype; y: [pairs, N] (row stride ldy) in y_dtype.
+TIB_API int tib_moe_expert_product(const void* x, int x_dtype, int64_t ldx, const void* w, int w_dtype, void* y, int y_dtype,
+                                   int64_t ldy, const int* offsets, const int* order, int pairs, int experts, int top,
+                                   int x_by_pair, int N, int K, int act, cudaStream_t stream) {
+  if (pairs == 0 || N == 0) return TIB_OK;
+  if (!x || !w || !y || !offsets || !order || pairs < 0 || N < 0 || K < 1 || top < 1) return TIB_E_ARG;
+  const int row_tiles = ceil_div(pairs, GM) + experts;      // at most this many tiles hold a row
+  if (row_tiles > 65535) return TIB_E_SIZE;
+  dim3 grid(ceil_div(N, GN), row_tiles);
+#define TIB_MOE_GO(TX, TW, TO)                                                                                             \
+  TIB_LAUNCH_DEPENDENT((moe_expert_product_kernel<TX, TW, TO>), grid, 256, 0, stream, (const TX*)x, ldx, (const TW*)w, (TO*)y, \
+                       ldy, offsets, order, experts, top, x_by_pair, N, K, act)
+  if (x_dtype == TIB_F32 && w_dtype == TIB_F32 && y_dtype == TIB_F32) TIB_MOE_GO(float, float, float);
+  else if (x_dtype == TIB_BF16 && w_dtype == TIB_BF16 && y_dtype == TIB_BF16) TIB_MOE_GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else if (x_dtype == TIB_BF16 && w_dtype == TIB_BF16 && y_dtype == TIB_F32) TIB_MOE_GO(__nv_bfloat16, __nv_bfloat16, float);
+  else return TIB_E_DTYPE;
+#undef TIB_MOE_GO
+  return TIB_OK;
+}
+
+// y: [pairs, width] fp32; shared: [tokens, width] in shared_dtype or null; gate: fp32 logit per token (stride ld_gate) or
+// null (the shared rows are added as they are); out: [tokens, width] in out_dtype.
+TIB_API int tib_moe_combine(const float* y, const int* place, const float* weights, int top, const void* shared,
+                            int shared_dtype, const float* gate, int64_t ld_gate, void* out, int out_dtype, int tokens,
+                            int width, cudaStream_t stream) {
+  if (tokens == 0 || width == 0) return TIB_OK;
+  if (!y || !place || !weights || !out || top < 1) return TIB_E_ARG;
+  const int threads = width >= 1024 ? 256 : 128;
+#define TIB_COMBINE_GO(TS, TO)                                                                                       \
+  TIB_LAUNCH_DEPENDENT((moe_combine_kernel<TS, TO>), tokens, threads, 0, stream, y, place, weights, top, (const TS*)shared, gate, \
+                       ld_gate, (TO*)out, width)
+  const int sd = shared ? shared_dtype : out_dtype;
+  if (sd == TIB_F32 && out_dtype == TIB_F32) TIB_COMBINE_GO(float, float);
+  else if (sd == TIB_BF16 && out_dtype == TIB_BF16) TIB_COMBINE_GO(__nv_bfloat16, __nv_bfloat16);
+  else if (sd == TIB_BF16 && out_dtype == TIB_F32) TIB_COMBINE_GO(__nv_bfloat16, float);
+  else if (sd == TIB_F32 && out_dtype == TIB_BF16) TIB_COMBINE_GO(float, __nv_bfloat16);
+  else return TIB_E_DTYPE;
+#undef TIB_COMBINE_GO
+  return TIB_OK;
+}

@@ -119,7 +119,11 @@ def lib() -> ctypes.CDLL:
                    "tib_blas_init", "tib_blas_gemm", "tib_gemm_tcgen05_2cta", "tib_gemm_tcgen05_2cta_supports",
                    "tib_gemm_tcgen05", "tib_gemm_tcgen05_supports",
                    "tib_gemm_tcgen05_swapab", "tib_gemm_tcgen05_swapab_supports", "tib_gemm_decode", "tib_gemm_decode_supports",
-                   "tib_plan_attention", "tib_plan_product"):
+                   "tib_plan_attention", "tib_plan_product", "tib_blas_gemm_batched",
+                   "tib_add_pair", "tib_unit_norm_add", "tib_sigmoid_gate", "tib_gelu_gate_table", "tib_relu_squared",
+                   "tib_scale_f32", "tib_pair_rows", "tib_add_vector", "tib_linear_attention", "tib_linear_attention_chunk",
+                   "tib_latent_append", "tib_latent_attention", "tib_moe_route", "tib_moe_group",
+                   "tib_moe_expert_product", "tib_moe_combine"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -254,9 +258,10 @@ def paged_attention_simt(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor,
 
 
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N] (fp32) = x[M, K] . w[N, K]^T with fp32 FMAs in fixed k order."""
-    _need(out, "out", torch.float32)
-    for name, t in (("x", x), ("w", w)):
+    """out[M, N] (fp32) = x[M, K] . w[N, K]^T with fp32 FMAs in fixed k order (rows of all three at any stride)."""
+    if out.dtype != torch.float32:
+        raise KernelError(f"out must be float32, got {out.dtype}")
+    for name, t in (("x", x), ("w", w), ("out", out)):
         if not t.is_cuda or t.stride(-1) != 1 or t.dim() != 2:
             raise KernelError(f"gemm_f32: {name} must be a 2-D CUDA tensor with unit inner stride")
     (m, k), (n, k2) = x.shape, w.shape
@@ -694,4 +699,284 @@ def prefill_attention_tcgen05(q: torch.Tensor, pool: torch.Tensor, out: torch.Te
         c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(q.numel() // (heads * head_dim)),
         c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(pool.shape[3]), c_int64(pool.stride(0)), c_int(pool.shape[0]),
         c_int(window), c_float(scale), c_int(int(skip_single)), _ptr(error_word), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Row-wise pieces of blocks other than the pre-norm one (csrc/gated_ops.cu).  Operands may be float32 or bfloat16
+# and may be column slices of a wider row (unit inner stride, any row stride).
+def _rows_of(t: torch.Tensor, name: str, width: int | None = None) -> None:
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be a 2-D CUDA tensor with unit inner stride")
+    if width is not None and t.shape[1] != width:
+        raise KernelError(f"{name} has {t.shape[1]} columns, wanted {width}")
+
+
+def add_pair(residual: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None = None,
+             copy: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += a + b in fp32 (``b`` may be None); ``copy``, if given, receives the new residual in its own type."""
+    _need(residual, "residual", torch.float32)
+    n, width = residual.shape
+    _rows_of(a, "a", width)
+    if b is not None:
+        _rows_of(b, "b", width)
+    if copy is not None:
+        _need(copy, "copy")
+        if copy.shape != residual.shape:
+            raise KernelError("add_pair: copy and residual differ in shape")
+    if a.shape[0] != n or (b is not None and b.shape[0] != n):
+        raise KernelError("add_pair: row counts differ")
+    _check("add_pair", lib().tib_add_pair(
+        _ptr(residual), _ptr(a), c_int(_code(a.dtype)), c_int64(a.stride(0)), _ptr(b),
+        c_int(_code(b.dtype) if b is not None else 0), c_int64(b.stride(0) if b is not None else 0), _ptr(copy),
+        c_int(_code(copy.dtype) if copy is not None else 0), c_int(n), c_int(width), _stream()))
+    return residual
+
+
+def unit_norm_add(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """residual += y / sqrt(mean(y^2) + eps) * weight, statistics and sum in fp32."""
+    _need(residual, "residual", torch.float32), _need(weight, "weight", torch.float32)
+    n, width = residual.shape
+    _rows_of(y, "y", width)
+    if y.shape[0] != n or weight.numel() != width:
+        raise KernelError("unit_norm_add: shapes do not fit")
+    _check("unit_norm_add", lib().tib_unit_norm_add(_ptr(residual), _ptr(y), c_int(_code(y.dtype)), c_int64(y.stride(0)),
+                                                    _ptr(weight), c_int(n), c_int(width), c_float(eps), _stream()))
+    return residual
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, weight: torch.Tensor | None = None,
+                 eps: float = 0.0) -> torch.Tensor:
+    """out = f(x) * sigmoid(gate) row by row; f is the RMS norm with ``weight`` when one is given, else the identity."""
+    _need(out, "out")
+    n, width = out.shape
+    _rows_of(x, "x", width), _rows_of(gate, "gate", width)
+    if weight is not None:
+        _need(weight, "weight", torch.float32)
+        if weight.numel() != width:
+            raise KernelError("sigmoid_gate: weight has the wrong length")
+    if x.shape[0] != n or gate.shape[0] != n:
+        raise KernelError("sigmoid_gate: row counts differ")
+    _check("sigmoid_gate", lib().tib_sigmoid_gate(
+        _ptr(x), c_int(_code(x.dtype)), c_int64(x.stride(0)), _ptr(gate), c_int(_code(gate.dtype)), c_int64(gate.stride(0)),
+        _ptr(weight), c_float(eps), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _stream()))
+    return out
+
+
+def gelu_gate_table(a: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, first: int, out: torch.Tensor) -> torch.Tensor:
+    """out[t, j] = gelu_tanh(a[t, j]) * table[ids[t], first + j]."""
+    _need(out, "out"), _need(ids, "ids", torch.int32)
+    n, width = out.shape
+    _rows_of(a, "a", width), _rows_of(table, "table")
+    if a.shape[0] != n or ids.numel() != n or first < 0 or first + width > table.shape[1]:
+        raise KernelError("gelu_gate_table: shapes do not fit")
+    _check("gelu_gate_table", lib().tib_gelu_gate_table(
+        _ptr(a), c_int(_code(a.dtype)), c_int64(a.stride(0)), _ptr(ids), _ptr(table), c_int(_code(table.dtype)),
+        c_int64(table.stride(0)), c_int(table.shape[0]), c_int(first), _ptr(out), c_int(_code(out.dtype)), c_int(n),
+        c_int(width), _stream()))
+    return out
+
+
+def relu_squared(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(x, "x"), _need(out, "out")
+    if x.numel() != out.numel():
+        raise KernelError("relu_squared: sizes differ")
+    _check("relu_squared", lib().tib_relu_squared(_ptr(x), c_int(_code(x.dtype)), _ptr(out), c_int(_code(out.dtype)),
+                                                  c_int64(x.numel()), _stream()))
+    return out
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor (fp32, in place)."""
+    _need(x, "x", torch.float32)
+    _check("scale", lib().tib_scale_f32(_ptr(x), c_float(factor), c_int64(x.numel()), _stream()))
+    return x
+
+
+def pair_rows(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = [x[t] ; y[t]] in out's type (x, y fp32)."""
+    _need(x, "x", torch.float32), _need(y, "y", torch.float32), _need(out, "out")
+    n, width = x.shape
+    if y.shape != x.shape or out.shape != (n, 2 * width):
+        raise KernelError("pair_rows: shapes do not fit")
+    _check("pair_rows", lib().tib_pair_rows(_ptr(x), _ptr(y), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _stream()))
+    return out
+
+
+def add_vector(x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """x[t] += v for every row (fp32)."""
+    _need(x, "x", torch.float32), _need(v, "v", torch.float32)
+    if v.numel() != x.shape[1]:
+        raise KernelError("add_vector: the vector has the wrong length")
+    _check("add_vector", lib().tib_add_vector(_ptr(x), _ptr(v), c_int(x.shape[0]), c_int(x.shape[1]), _stream()))
+    return x
+
+
+# ---------------------------------------------------------------------------
+def library_gemm_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, w_kn: bool) -> torch.Tensor:
+    """out[:, b, :] = x[:, b, :] . w[b]^T for every b, by one cuBLAS call.  ``x``: [M, B, K] and ``out``: [M, B, N] are views
+    with unit inner stride whose rows (M) and batches (B) lie at any strides; ``w``: [B, N, K], or [B, K, N] when ``w_kn``."""
+    library_gemm_ready(x.device)
+    m, batch, k = x.shape
+    n = w.shape[2] if w_kn else w.shape[1]
+    if w.shape[0] != batch or (w.shape[1] if w_kn else w.shape[2]) != k or out.shape != (m, batch, n):
+        raise KernelError(f"library_gemm_batched: shapes {tuple(x.shape)}, {tuple(w.shape)} (kn={w_kn}), {tuple(out.shape)} do not fit")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.stride(2) != 1 or w.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError("library_gemm_batched: bf16 operands with unit inner stride are needed")
+    status = lib().tib_blas_gemm_batched(
+        _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)), c_int64(w.stride(1)),
+        c_int64(out.stride(0)), c_int64(x.stride(1)), c_int64(w.stride(0)), c_int64(out.stride(1)), c_int(batch),
+        c_int(1 if w_kn else 0), c_int(_code(out.dtype)), _stream())
+    if status:
+        raise KernelError(f"library_gemm_batched: status {status} (20000 + n: cuBLAS status n)")
+    return out
+
+
+# ---------------------------------------------------------------------------
+def linear_attention_chunk(key_dim: int, value_dim: int) -> int:
+    """Tokens per chunk of the decayed linear attention kernel for these head sizes (0: they do not fit an SM)."""
+    return int(lib().tib_linear_attention_chunk(c_int(key_dim), c_int(value_dim)))
+
+
+def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
+                     powers: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, n_entries: int, heads: int,
+                     key_dim: int, value_dim: int, *, silu: bool) -> torch.Tensor:
+    """o_t = S_t^T q_t with S_t = decay * S_(t-1) + k_t v_t^T per head, over the ragged batch; ``state``
+    [slots, heads, key_dim, value_dim] (fp32) is read and left updated; ``powers`` [heads, chunk + 1] holds decay^m."""
+    for name, t, width in (("q", q, heads * key_dim), ("k", k, heads * key_dim), ("v", v, heads * value_dim)):
+        _rows_of(t, name, width)
+        if t.dtype != q.dtype:
+            raise KernelError("linear_attention: q, k and v differ in type")
+    _need(out, "out", torch.float32), _need(state, "state", torch.float32), _need(powers, "powers", torch.float32)
+    _need(q_start, "q_start", torch.int32), _need(slots, "slots", torch.int32)
+    chunk = powers.shape[1] - 1
+    if out.shape != (q.shape[0], heads * value_dim) or tuple(state.shape[1:]) != (heads, key_dim, value_dim) or powers.shape[0] != heads:
+        raise KernelError("linear_attention: out, state or powers do not fit the head sizes")
+    if q_start.numel() < n_entries + 1 or slots.numel() < n_entries:
+        raise KernelError("linear_attention: entry arrays are shorter than n_entries")
+    _check("linear_attention", lib().tib_linear_attention(
+        _ptr(q), _ptr(k), _ptr(v), c_int64(q.stride(0)), c_int64(k.stride(0)), c_int64(v.stride(0)), _ptr(out), _ptr(state),
+        _ptr(powers), _ptr(q_start), _ptr(slots), c_int(n_entries), c_int(heads), c_int(key_dim), c_int(value_dim),
+        c_int(chunk), c_int(1 if silu else 0), c_int(_code(q.dtype)), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+def latent_append(dkv: torch.Tensor, q: torch.Tensor, folded: torch.Tensor, keys: torch.Tensor | None,
+                  positions: torch.Tensor, token_slot: torch.Tensor | None, block_table: torch.Tensor | None,
+                  norm_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, heads: int, dim: int, rank: int, rot: int,
+                  error_word: torch.Tensor | None = None) -> None:
+    """Norm the latent, rotate the shared key part and store both in the tokens' pages (``keys``: [pages, 1, page_size,
+    rank + rot], or None to store nothing); rotate every head's query part into ``folded[..., rank:]``."""
+    _rows_of(dkv, "dkv", rank + rot), _rows_of(q, "q", heads * (dim + rot))
+    _need(folded, "folded", torch.float32), _need(positions, "positions", torch.int32)
+    _need(norm_weight, "norm_weight", torch.float32), _need(inv_freq, "inv_freq", torch.float32)
+    n = dkv.shape[0]
+    if q.dtype != dkv.dtype or q.shape[0] != n or folded.shape != (n, heads, rank + rot) or norm_weight.numel() != rank:
+        raise KernelError("latent_append: shapes or types do not fit")
+    page_size = page_stride = num_pages = table_stride = 0
+    if keys is not None:
+        if token_slot is None or block_table is None:
+            raise KernelError("latent_append: token_slot and block_table are needed to write the cache")
+        _need(token_slot, "token_slot", torch.int32), _need(block_table, "block_table", torch.int32)
+        if keys.dtype != dkv.dtype or keys.dim() != 4 or keys.shape[1] != 1 or keys.shape[3] != rank + rot or keys.stride(3) != 1 \
+                or keys.stride(2) != rank + rot:
+            raise KernelError(f"latent_append: pages of shape {tuple(keys.shape)} do not fit")
+        num_pages, page_size, page_stride, table_stride = keys.shape[0], keys.shape[2], keys.stride(0), block_table.stride(0)
+    _check("latent_append", lib().tib_latent_append(
+        _ptr(dkv), c_int64(dkv.stride(0)), _ptr(q), c_int64(q.stride(0)), _ptr(keys), _ptr(folded), _ptr(positions),
+        _ptr(token_slot), _ptr(block_table), c_int(table_stride), _ptr(norm_weight), c_float(eps), _ptr(inv_freq),
+        c_int(inv_freq.numel()), c_int(n), c_int(heads), c_int(dim), c_int(rank), c_int(rot), c_int(page_size),
+        c_int64(page_stride), c_int(num_pages), _ptr(error_word), c_int(_code(dkv.dtype)), _stream()))
+
+
+def latent_attention(folded: torch.Tensor, keys: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor, kv_start: torch.Tensor,
+                     slots: torch.Tensor, block_table: torch.Tensor, n_entries: int, max_q_len: int, heads: int, rank: int,
+                     rot: int, scale: float, error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of folded queries [tokens, heads, rank + rot] (fp32) over paged latent rows; the value of a
+    key is its first ``rank`` elements.  ``out``: [tokens, heads, rank] fp32."""
+    _need(folded, "folded", torch.float32), _need(out, "out", torch.float32)
+    for name, t in (("q_start", q_start), ("kv_start", kv_start), ("slots", slots), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    n = folded.shape[0]
+    if folded.shape != (n, heads, rank + rot) or out.shape != (n, heads, rank):
+        raise KernelError("latent_attention: folded / out do not fit the sizes")
+    if keys.dim() != 4 or keys.shape[1] != 1 or keys.shape[3] != rank + rot or keys.stride(3) != 1 or keys.stride(2) != rank + rot:
+        raise KernelError(f"latent_attention: pages of shape {tuple(keys.shape)} do not fit")
+    if q_start.numel() < n_entries + 1 or kv_start.numel() < n_entries or slots.numel() < n_entries:
+        raise KernelError("latent_attention: entry arrays are shorter than n_entries")
+    _check("latent_attention", lib().tib_latent_attention(
+        _ptr(folded), _ptr(keys), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(rank), c_int(rot),
+        c_int(keys.shape[2]), c_int64(keys.stride(0)), c_int(keys.shape[0]), c_float(scale), _ptr(error_word),
+        c_int(_code(keys.dtype)), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+MOE_ACT = {"none": 0, "relu2": 1, "silu": 2}
+
+
+def moe_route(logits: torch.Tensor, experts: int, top: int, ids: torch.Tensor, weights: torch.Tensor, *,
+              sigmoid_scores: bool = False, normalize: bool = True, norm_eps: float = 0.0) -> None:
+    """From fp32 router logits (the first ``experts`` columns of ``logits``): the ``top`` best experts of every token and
+    their weights."""
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1 or logits.shape[1] < experts:
+        raise KernelError("moe_route: logits must be 2-D fp32 with unit inner stride and at least `experts` columns")
+    _need(ids, "ids", torch.int32), _need(weights, "weights", torch.float32)
+    n = logits.shape[0]
+    if ids.shape != (n, top) or weights.shape != (n, top):
+        raise KernelError("moe_route: ids / weights must be [tokens, top]")
+    _check("moe_route", lib().tib_moe_route(_ptr(logits), c_int64(logits.stride(0)), c_int(n), c_int(experts), c_int(top),
+                                            c_int(int(sigmoid_scores)), c_int(int(normalize)), c_float(norm_eps), _ptr(ids),
+                                            _ptr(weights), _stream()))
+
+
+def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """Sort the (token, choice) pairs by expert on the device: offsets [experts + 1], order[sorted] = pair, place[pair] = sorted."""
+    for name, t in (("ids", ids), ("offsets", offsets), ("order", order), ("place", place)):
+        _need(t, name, torch.int32)
+    pairs = ids.numel()
+    if offsets.numel() != experts + 1 or order.numel() != pairs or place.numel() != pairs:
+        raise KernelError("moe_group: array lengths do not fit")
+    _check("moe_group", lib().tib_moe_group(_ptr(ids), c_int(pairs), c_int(experts), _ptr(offsets), _ptr(order), _ptr(place), _stream()))
+
+
+def moe_expert_product(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, top: int,
+                       *, x_by_pair: bool, act: str = "none") -> torch.Tensor:
+    """y[s] = act(x[source of s] . w[expert of s]^T) for the sorted rows s; ``w``: [experts, N, K]; ``x_by_pair``: the source
+    of sorted row s is token order[s] // top, else row s itself."""
+    _rows_of(x, "x"), _need(w, "w"), _rows_of(y, "y")
+    experts, n, k = w.shape
+    pairs = order.numel()
+    if x.shape[1] != k or y.shape != (pairs, n) or offsets.numel() != experts + 1:
+        raise KernelError("moe_expert_product: shapes do not fit")
+    _check("moe_expert_product", lib().tib_moe_expert_product(
+        _ptr(x), c_int(_code(x.dtype)), c_int64(x.stride(0)), _ptr(w), c_int(_code(w.dtype)), _ptr(y), c_int(_code(y.dtype)),
+        c_int64(y.stride(0)), _ptr(offsets), _ptr(order), c_int(pairs), c_int(experts), c_int(top), c_int(int(x_by_pair)),
+        c_int(n), c_int(k), c_int(MOE_ACT[act]), _stream()))
+    return y
+
+
+def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, shared: torch.Tensor | None = None,
+                gate: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = sum_k weights[t, k] * y[place[t, k]] (+ sigmoid(gate[t]) * shared[t]); ``gate``: one fp32 logit per token
+    (a column view is fine)."""
+    _need(y, "y", torch.float32), _need(place, "place", torch.int32), _need(weights, "weights", torch.float32), _need(out, "out")
+    n, width = out.shape
+    top = weights.shape[1]
+    if y.shape[1] != width or weights.shape[0] != n or place.numel() != n * top:
+        raise KernelError("moe_combine: shapes do not fit")
+    if shared is not None:
+        _need(shared, "shared")
+        if shared.shape != out.shape:
+            raise KernelError("moe_combine: shared rows do not fit")
+    ld_gate = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.shape[0] != n:
+            raise KernelError("moe_combine: gate must hold one fp32 logit per token")
+        ld_gate = gate.stride(0)
+    _check("moe_combine", lib().tib_moe_combine(
+        _ptr(y), _ptr(place), _ptr(weights), c_int(top), _ptr(shared), c_int(_code(shared.dtype) if shared is not None else 0),
+        _ptr(gate), c_int64(ld_gate), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _stream()))
     return out

@@ -14,7 +14,7 @@ import torch
 
 from torchinferno_b200.kernels import gemm, ops
 from torchinferno_b200.kernels.gemm import linear
-from torchinferno_b200.models.spec import ModelSpec
+from torchinferno_b200.models.spec import ModelSpec, StageCall
 from torchinferno_b200.parts.base import (Block, CacheSpec, KVBinding, LayerContext, ResidualStream,
                                           StateSpec, WeightSpec, build_part)
 
@@ -31,8 +31,21 @@ class CausalLM:
         self.final_norm = build_part("norm", spec.final_norm, dtype=dtype, device=self.device)
         self.after_embedding = None if spec.after_embedding is None else \
             build_part("stream_stage", spec.after_embedding, dtype=dtype, device=self.device)
+        self.stages = [build_part("stream_stage", stage, dtype=dtype, device=self.device) for stage in spec.stages]
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
+
+    def _owned_parts(self):
+        """(full name prefix, part) of every part that owns weights, blocks first."""
+        spec = self.spec
+        for layer, block in zip(spec.layers, self.blocks):
+            for prefix, part in block.named_parts():
+                yield layer.prefix + prefix, part
+        yield spec.final_norm.prefix, self.final_norm
+        if self.after_embedding is not None:
+            yield spec.after_embedding.prefix, self.after_embedding
+        for stage_spec, stage in zip(spec.stages, self.stages):
+            yield stage_spec.prefix, stage
 
     # ------------------------------------------------------------ weights
     def expected_tensors(self) -> dict[str, WeightSpec]:
@@ -40,15 +53,14 @@ class CausalLM:
         spec = self.spec
         expected: dict[str, WeightSpec] = {
             spec.embedding_name: WeightSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size))}
-        for layer, block in zip(spec.layers, self.blocks):
-            for prefix, part in block.named_parts():
-                for ws in part.weight_specs():
-                    name = layer.prefix + prefix + ws.name
-                    expected[name] = WeightSpec(name, ws.shape, ws.init, ws.std, ws.role, ws.optional)
-        for part, part_spec in ((self.final_norm, spec.final_norm), (self.after_embedding, spec.after_embedding)):
-            for ws in (part.weight_specs() if part is not None else ()):
-                name = part_spec.prefix + ws.name
+        for prefix, part in self._owned_parts():
+            for ws in part.weight_specs():
+                name = prefix + ws.name
                 expected[name] = WeightSpec(name, ws.shape, ws.init, ws.std, ws.role, ws.optional)
+            for ws in part.shared_weight_specs():
+                if ws.name in expected and tuple(expected[ws.name].shape) != tuple(ws.shape):
+                    raise ValueError(f"{ws.name}: parts that share it declare shapes {expected[ws.name].shape} and {ws.shape}")
+                expected[ws.name] = ws
         if spec.head_name is not None:
             expected[spec.head_name] = WeightSpec(
                 spec.head_name, (spec.vocab_size, spec.hidden_size), optional=spec.tie_head_to_embedding)
@@ -74,17 +86,12 @@ class CausalLM:
             # An untied model whose file has no head is refused on purpose: guessing that the embedding
             # doubles as the head would turn a truncated checkpoint into silently wrong logits.
             raise KeyError(f"{spec.head_name}: the model does not tie its head to the embedding, and no head was given")
-        for layer, block in zip(spec.layers, self.blocks):
-            for prefix, part in block.named_parts():
-                full = layer.prefix + prefix
-                part.bind({ws.name: take(full + ws.name) for ws in part.weight_specs()
-                           if full + ws.name in tensors})
-        self.final_norm.bind({ws.name: take(spec.final_norm.prefix + ws.name)
-                              for ws in self.final_norm.weight_specs()})
-        if self.after_embedding is not None:
-            self.after_embedding.bind({ws.name: take(spec.after_embedding.prefix + ws.name)
-                                       for ws in self.after_embedding.weight_specs()
-                                       if spec.after_embedding.prefix + ws.name in tensors})
+        shared_names = {ws.name for _, part in self._owned_parts() for ws in part.shared_weight_specs()}
+        shared = {name: take(name) for name in shared_names if name in tensors}
+        for full, part in self._owned_parts():
+            own = {ws.name: take(full + ws.name) for ws in part.weight_specs() if full + ws.name in tensors}
+            own.update({ws.name: shared[ws.name] for ws in part.shared_weight_specs() if ws.name in shared})
+            part.bind(own)
         if self.device.type == "cuda":
             gemm.tune_few_rows()      # weights that left the choice of their few-rows kernel open get it now
 
@@ -97,8 +104,7 @@ class CausalLM:
                 seen[t.data_ptr()] = t.numel() * t.element_size()
 
         note(self.head)
-        parts = [part for block in self.blocks for _, part in block.named_parts()] + [self.final_norm]
-        for part in parts:
+        for _, part in self._owned_parts():
             for key, value in vars(part).items():
                 if key.endswith("weight"):
                     note(getattr(value, "tensor", value) if not isinstance(value, torch.Tensor) else value)
@@ -109,7 +115,7 @@ class CausalLM:
         """CacheSpec of every cache layer, in cache-layer order."""
         needs: dict[int, CacheSpec] = {}
         for call in self.spec.schedule:
-            if call.cache is None:
+            if isinstance(call, StageCall) or call.cache is None:
                 continue
             cs = self.blocks[call.layer].mixer.cache_spec()
             if cs is None:
@@ -121,12 +127,14 @@ class CausalLM:
 
     def capturable(self) -> bool:
         """Whether a decode step of this model may be captured in a CUDA graph (see ``Mixer.capturable``)."""
-        parts = [block.mixer for block in self.blocks] + ([self.after_embedding] if self.after_embedding is not None else [])
+        parts = [block.mixer for block in self.blocks] + ([self.after_embedding] if self.after_embedding is not None else []) \
+            + list(self.stages)
         return all(getattr(part, "capturable", getattr(part, "state_spec", lambda: None)() is None) for part in parts)
 
     def state_requirements(self) -> list[StateSpec | None]:
         """StateSpec of every layer call of the schedule (None where the mixer has none)."""
-        return [self.blocks[call.layer].mixer.state_spec() for call in self.spec.schedule]
+        return [None if isinstance(call, StageCall) else self.blocks[call.layer].mixer.state_spec()
+                for call in self.spec.schedule]
 
     # ------------------------------------------------------------ forward
     def forward(self, batch, cache) -> torch.Tensor:
@@ -135,9 +143,15 @@ class CausalLM:
         residual = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(batch.token_ids, self.embedding, residual)
         stream = ResidualStream(residual, self.dtype)
+        if self.spec.keeps_embedding_output:
+            stream.origin = residual.clone()
         if self.after_embedding is not None:
             self.after_embedding.forward(stream, LayerContext(batch=batch, error_word=cache.error_word, layer_index=-1))
         for index, call in enumerate(self.spec.schedule):
+            if isinstance(call, StageCall):
+                self.stages[call.stage].forward(stream, LayerContext(batch=batch, error_word=cache.error_word,
+                                                                     layer_index=index, call_arg=call.arg))
+                continue
             kv = None
             if call.cache is not None:
                 kv = cache.kv_binding(call.cache)
@@ -148,4 +162,7 @@ class CausalLM:
         if batch.n_logits == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         rows = stream.normed(self.final_norm, batch.logit_rows)
-        return linear(rows, self.head, out_dtype=torch.float32)
+        logits = linear(rows, self.head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0:
+            ops.scale_(logits, self.spec.logit_scale)
+        return logits

@@ -4,7 +4,10 @@
 order of execution: a list of :class:`LayerCall` that may name a layer twice
 and says which cache layer the call uses; a call with ``writes_cache=False``
 reads what an earlier call stored there.  ``cache_layers`` is the number of
-distinct cache layers the schedule addresses.
+distinct cache layers the schedule addresses.  Between layer calls the schedule
+may name a stage (:class:`StageCall`): a part of category ``stream_stage`` from
+``stages`` that works on the residual stream, with an integer argument (the
+number of a pass over a range of layers that runs several times, say).
 """
 from __future__ import annotations
 
@@ -28,6 +31,12 @@ class LayerCall:
 
 
 @dataclass(frozen=True)
+class StageCall:
+    stage: int                      # index into ModelSpec.stages
+    arg: int = 0                    # handed to the stage as ``ctx.call_arg``
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     architecture: str
     hidden_size: int
@@ -35,20 +44,26 @@ class ModelSpec:
     max_positions: int
     embedding_name: str             # tensor name of the [vocab, hidden] table
     layers: tuple[BlockSpec, ...]
-    schedule: tuple[LayerCall, ...]
+    schedule: tuple["LayerCall | StageCall", ...]
     final_norm: PartSpec            # prefix holds its full name prefix
     head_name: str | None           # tensor name of the [vocab, hidden] output matrix
     tie_head_to_embedding: bool = False
     after_embedding: PartSpec | None = None   # category "stream_stage"; prefix holds its full name prefix
     config: Mapping[str, Any] = field(default_factory=dict)  # the config.json this came from
+    stages: tuple[PartSpec, ...] = ()         # category "stream_stage"; each prefix is a full name prefix
+    logit_scale: float = 1.0                  # the head's output is multiplied by this
+    keeps_embedding_output: bool = False      # stages read the embedding output (``ResidualStream.origin``)
 
     def __post_init__(self) -> None:
         for call in self.schedule:
-            if not 0 <= call.layer < len(self.layers):
+            if isinstance(call, StageCall):
+                if not 0 <= call.stage < len(self.stages):
+                    raise ValueError(f"schedule names stage {call.stage}, but there are {len(self.stages)}")
+            elif not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {call.layer}, but there are {len(self.layers)}")
         written: set[int] = set()
         for call in self.schedule:
-            if call.cache is None:
+            if isinstance(call, StageCall) or call.cache is None:
                 continue
             if call.writes_cache:
                 if call.cache in written:
@@ -59,5 +74,5 @@ class ModelSpec:
 
     @property
     def cache_layers(self) -> int:
-        ids = [call.cache for call in self.schedule if call.cache is not None]
+        ids = [call.cache for call in self.schedule if isinstance(call, LayerCall) and call.cache is not None]
         return max(ids) + 1 if ids else 0

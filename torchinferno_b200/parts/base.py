@@ -98,6 +98,7 @@ class LayerContext:
     state: torch.Tensor | None = None   # [slots, *StateSpec.shape] of this layer, or None
     error_word: torch.Tensor | None = None
     layer_index: int = 0
+    call_arg: int = 0                   # the argument of a stage call of the schedule
 
 
 class ResidualStream:
@@ -112,6 +113,10 @@ class ResidualStream:
         self.residual = residual        # [tokens, hidden] float32
         self.pending: torch.Tensor | None = None
         self.dtype = dtype              # activation dtype of normalised rows
+        self.origin: torch.Tensor | None = None    # the embedding output, kept when the model's stages read it
+        # the residual rows in the activation type, left by whoever last changed the residual and had them at
+        # hand; whoever changes the residual next drops it
+        self.activation_copy: torch.Tensor | None = None
 
     def normed(self, norm: "Norm", rows: torch.Tensor | None = None) -> torch.Tensor:
         n = self.residual.shape[0] if rows is None else rows.numel()
@@ -128,6 +133,15 @@ class ResidualStream:
         if self.pending is not None:
             raise RuntimeError("a delta is already pending; a norm must fold it in first")
         self.pending = delta
+        self.activation_copy = None
+
+    def settle(self) -> torch.Tensor:
+        """Fold a pending delta into the residual (for a part that reads the residual itself); returns the residual."""
+        if self.pending is not None:
+            from torchinferno_b200.kernels import ops
+            ops.add_pair(self.residual, self.pending)
+            self.pending = None
+        return self.residual
 
 
 # --------------------------------------------------------------- interfaces
@@ -139,6 +153,11 @@ class Part:
         self.device = device
 
     def weight_specs(self) -> list[WeightSpec]:
+        return []
+
+    def shared_weight_specs(self) -> list[WeightSpec]:
+        """Tensors this part reads that are not its own: named in full (no prefix is put before them), declared
+        alike by every part that reads them, loaded once and handed to each in :meth:`bind` under that name."""
         return []
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
@@ -238,4 +257,5 @@ def _ensure_builtin() -> None:
     if _loaded:
         return
     _loaded = True
-    from torchinferno_b200.parts import attention, block, mlp, norm, rope  # noqa: F401
+    from torchinferno_b200.parts import (attention, block, latent_attention, linear_attention, mlp, moe, norm,  # noqa: F401
+                                         parallel_block, rope, stream_stages)

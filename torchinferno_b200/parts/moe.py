@@ -1,0 +1,95 @@
+"""Routed feed-forward: every token goes through the ``top`` best of ``experts`` small feed-forwards.
+
+Router logits z = W_router x in fp32; scores = softmax(z) over all experts (or sigmoid(z)); the ``top`` largest
+are chosen (lowest index first among equals); their weights are the scores, divided by their sum plus
+``norm_eps`` when ``normalize``.  An expert is W_down act(W_up x) with act = relu squared (or silu), no biases;
+the output is the weighted sum of the chosen experts' outputs.  An optional shared expert of the same form
+runs for every token and is added, multiplied by sigmoid(w_sg . x) when it has a gate row.
+
+The pairs (token, choice) are sorted by expert on the device and both products run over the sorted rows
+(csrc/moe.cu); no count comes back to the host, so a step with this part may be captured.
+"""
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from torchinferno_b200.kernels import ops
+from torchinferno_b200.kernels.gemm import LinearWeight, linear
+from torchinferno_b200.parts.base import FeedForward, LayerContext, WeightSpec, register_part
+
+
+class RoutedExperts(FeedForward):
+    def __init__(self, *, hidden_size: int, experts: int, top: int, expert_size: int, activation: str = "relu2",
+                 scores: str = "softmax", normalize: bool = True, norm_eps: float = 0.0, shared_size: int = 0,
+                 shared_gate: bool = False, router_name: str = "router", expert_prefix: str = "e", up_name: str = "up",
+                 down_name: str = "down", shared_prefix: str = "shared.", shared_gate_name: str = "sg",
+                 dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        if not 1 <= top <= experts:
+            raise ValueError("top must be between 1 and the number of experts")
+        if activation not in ("relu2", "silu") or scores not in ("softmax", "sigmoid"):
+            raise ValueError(f"unknown activation {activation!r} or scores {scores!r}")
+        self.hidden_size, self.experts, self.top, self.expert_size = hidden_size, experts, top, expert_size
+        self.activation, self.scores, self.normalize, self.norm_eps = activation, scores, bool(normalize), float(norm_eps)
+        self.shared_size, self.shared_gate = int(shared_size or 0), bool(shared_gate and shared_size)
+        self.names = (router_name, expert_prefix, up_name, down_name, shared_prefix, shared_gate_name)
+
+    def _expert(self, e: int, which: str) -> str:
+        _, prefix, up, down, _, _ = self.names
+        return f"{prefix}{e}.{up if which == 'up' else down}"
+
+    def weight_specs(self) -> list[WeightSpec]:
+        router, _, up, down, shared, gate = self.names
+        specs = [WeightSpec(router, (self.experts, self.hidden_size))]
+        for e in range(self.experts):
+            specs += [WeightSpec(self._expert(e, "up"), (self.expert_size, self.hidden_size)),
+                      WeightSpec(self._expert(e, "down"), (self.hidden_size, self.expert_size))]
+        if self.shared_size:
+            specs += [WeightSpec(shared + up, (self.shared_size, self.hidden_size)),
+                      WeightSpec(shared + down, (self.hidden_size, self.shared_size))]
+            if self.shared_gate:
+                specs.append(WeightSpec(shared + gate, (1, self.hidden_size)))
+        return specs
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        router, _, up, down, shared, gate = self.names
+        rows = [weights[router]] + ([weights[shared + gate]] if self.shared_gate else [])
+        self.router_weight = torch.cat(rows, dim=0).to(torch.float32).contiguous()      # (the router is fp32 in both modes)
+        self.up_weight = torch.stack([weights[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
+        self.down_weight = torch.stack([weights[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
+        if self.shared_size:
+            self.shared_up_weight = LinearWeight(weights[shared + up], few_rows_tcgen05=None)
+            self.shared_down_weight = LinearWeight(weights[shared + down], few_rows_tcgen05=None)
+
+    def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
+        n, dev, top = x.shape[0], x.device, self.top
+        logits = torch.empty((n, self.router_weight.shape[0]), dtype=torch.float32, device=dev)
+        ops.gemm_f32(x, self.router_weight, logits)
+        ids = torch.empty((n, top), dtype=torch.int32, device=dev)
+        weights = torch.empty((n, top), dtype=torch.float32, device=dev)
+        ops.moe_route(logits, self.experts, top, ids, weights, sigmoid_scores=self.scores == "sigmoid",
+                      normalize=self.normalize, norm_eps=self.norm_eps)
+        offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=dev)
+        order = torch.empty(n * top, dtype=torch.int32, device=dev)
+        place = torch.empty(n * top, dtype=torch.int32, device=dev)
+        ops.moe_group(ids, self.experts, offsets, order, place)
+        inner = torch.empty((n * top, self.expert_size), dtype=x.dtype, device=dev)
+        ops.moe_expert_product(x, self.up_weight, inner, offsets, order, top, x_by_pair=True, act=self.activation)
+        outer = torch.empty((n * top, self.hidden_size), dtype=torch.float32, device=dev)
+        ops.moe_expert_product(inner, self.down_weight, outer, offsets, order, top, x_by_pair=False)
+        shared_rows = None
+        if self.shared_size:
+            hidden = linear(x, self.shared_up_weight)
+            if self.activation == "relu2":
+                ops.relu_squared(hidden, hidden)
+            else:
+                raise NotImplementedError("a shared expert with silu")
+            shared_rows = linear(hidden, self.shared_down_weight)
+        out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=dev)
+        gate = logits[:, self.experts] if self.shared_gate else None
+        return ops.moe_combine(outer, place, weights, out, shared_rows, gate)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)
