@@ -412,6 +412,94 @@ def run_ours(args) -> dict:
     return record
 
 
+# ------------------------------------------------------ another design beside Llama
+# Layer sizes that resemble a real model's (width 2048, heads of 128, a latent of 512 + 64 rotated, experts of 1024),
+# four layers of each design, the closest Llama at equal width, head count and feed-forward size beside them.
+DESIGN_WIDTH, DESIGN_HEADS, DESIGN_VOCAB, DESIGN_LAYERS = 2048, 16, 32000, 4
+
+
+def design_configs() -> dict:
+    latent = {"heads": DESIGN_HEADS, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+              "rot": {"base": 500000.0, "dims": 64}}
+    lightning = {"heads": DESIGN_HEADS, "dim": 128, "vdim": 128, "decay": [1 - 2.0 ** -(3 + i % 6) for i in range(DESIGN_HEADS)]}
+    dense = {"kind": "dense", "ff": 8192}
+    routed = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": 1024}, "shared": {"ff": 2048}}
+    # (a loop of one pass: four layer runs, as the Llama beside it has, with the pass's input product once)
+    zipedra = {"architecture": "Zipedra", "vocab": DESIGN_VOCAB, "width": DESIGN_WIDTH, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+               "token_side": {"dim": 64}, "loop": {"start": 1, "stop": 3, "times": 1},
+               "layers": [{"type": "latent_attention", "mixer": latent, "mlp": dense},
+                          {"type": "lightning", "mixer": lightning, "mlp": routed},
+                          {"type": "latent_attention", "mixer": latent, "mlp": routed},
+                          {"type": "lightning", "mixer": lightning, "mlp": dense}]}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": DESIGN_VOCAB, "hidden_size": DESIGN_WIDTH,
+             "intermediate_size": 8192, "num_hidden_layers": DESIGN_LAYERS, "num_attention_heads": DESIGN_HEADS,
+             "num_key_value_heads": 8, "head_dim": 128, "max_position_embeddings": 8192, "rope_theta": 500000.0,
+             "rope_scaling": None, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+    return {"zipedra": zipedra, "llama": llama}
+
+
+def run_design(args) -> dict:
+    """Prefill and decode throughput of the Zipedra design at layer sizes that resemble a real model's, beside the
+    closest Llama of equal width, and its own kernels alone beside the like kernels of Llama, each against the roofline."""
+    import contextlib
+    import io
+    import torch
+    from torchinferno_b200 import bench_kernels
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.engine.factory import make_runner, random_model
+    from torchinferno_b200.kernels.library import load_library
+    load_library()
+    prompt_len, batch, steps = 2048, args.batch, min(args.steps, 64)
+    points = {}
+    with torch.inference_mode():
+        for name, config in design_configs().items():
+            model = random_model(config, seed=0, dtype="bfloat16")
+            runner = make_runner(model, page_size=PAGE_SIZE, max_tokens=(batch + 1) * (prompt_len + 256), max_requests=batch + 1,
+                                 max_request_tokens=prompt_len + 256, check_errors=False)
+            g = torch.Generator().manual_seed(5)
+            times = []
+            for it in range(6):
+                prompt = torch.randint(0, model.spec.vocab_size, (prompt_len,), generator=g).tolist()
+                begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                begin.record()
+                runner.step([StepEntry(f"p{it}", prompt, [prompt_len - 1])])
+                end.record()
+                torch.cuda.synchronize()
+                runner.end([f"p{it}"])
+                if it >= 3:
+                    times.append(begin.elapsed_time(end))
+            points[f"{name}_prefill_tok_s"] = round(prompt_len / (statistics.median(times) / 1e3), 1)
+            points[f"{name}_prefill_ms"] = round(statistics.median(times), 3)
+            prompts = torch.randint(0, model.spec.vocab_size, (batch, prompt_len), generator=g).tolist()
+            ids = [f"d{i}" for i in range(batch)]
+            first = prefill_requests(runner, ids, prompts, prompt_len)
+            drawn = runner.decode_loop(ids, first, max(3, args.warmup), temperature=[0.0] * batch, seeds=list(range(batch)))
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            runner.decode_loop(ids, drawn[-1].tolist(), steps)
+            end.record()
+            torch.cuda.synchronize()
+            ms = begin.elapsed_time(end)
+            points[f"{name}_decode_b{batch}_tok_s"] = round(batch * steps / (ms / 1e3), 1)
+            points[f"{name}_decode_b{batch}_ms_per_step"] = round(ms / steps, 4)
+            points[f"{name}_weight_gb"] = round(model.weight_bytes() / 1e9, 3)
+            runner.end(ids)
+            del runner, model
+            torch.cuda.empty_cache()
+        lines = io.StringIO()
+        with contextlib.redirect_stdout(lines):
+            for argv in (["latent-attention"], ["prefill-attention", "--heads", "16", "--kv-heads", "8"],
+                         ["decode-attention", "--heads", "16", "--kv-heads", "8"], ["linear-attention"], ["expert-product"]):
+                bench_kernels.main(argv)
+    kernels = [json.loads(line) for line in lines.getvalue().splitlines() if line.startswith("{")]
+    return {"design": "zipedra", "beside": "llama", "dtype": "bf16", "data": "synthetic token ids, random weights",
+            "config": {"width": DESIGN_WIDTH, "heads": DESIGN_HEADS, "layer_runs": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
+                       "prompt_len": prompt_len, "batch": batch, "decode_steps": steps, "page_size": PAGE_SIZE},
+            "points": points, "kernels": kernels}
+
+
 # -------------------------------------------------------------- reference
 def run_reference(args) -> dict:
     """The unmodified reference from baseline/_ref: its Llama3PipelineForCausalLM.generate on the same sizes."""
@@ -508,6 +596,9 @@ def main(argv=None) -> int:
     parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
     parser.add_argument("--workloads", nargs="*", default=list(WORKLOADS), choices=list(WORKLOADS),
                         help="serving workloads of the smaller sizes to add to points")
+    parser.add_argument("--design", choices=["zipedra"], default=None,
+                        help="instead of the headline run: prefill and decode throughput of this design at layer sizes that "
+                             "resemble a real model's, beside the closest Llama, and its kernels against the roofline")
     args = parser.parse_args(argv)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
@@ -516,6 +607,9 @@ def main(argv=None) -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design is not None:
+        print(json.dumps(run_design(args)))
+        return 0
     if args.point_steps is None:
         args.point_steps = args.steps
     if PROMPT_LEN + args.warmup + max(args.steps, args.point_steps) + 1 > CONTEXT + PAGE_SIZE:

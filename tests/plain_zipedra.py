@@ -110,14 +110,19 @@ def squared_relu_expert(h, up, down):
     return torch.relu(h @ up.T).pow(2) @ down.T
 
 
-def routed_feed_forward(h, w, p, mlp):
+def routed_feed_forward(h, w, p, mlp, gaps=None):
     """softmax over all experts, the ``top`` largest chosen (lowest index first among equals), their scores
-    divided by their sum (+ 1e-20) as weights; plus a shared expert gated by one sigmoid per token."""
+    divided by their sum (+ 1e-20) as weights; plus a shared expert gated by one sigmoid per token.
+    ``gaps`` (a list per token) collects how far the last chosen score lies above the first one left out, as a
+    share of itself."""
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
     scores = torch.softmax(h @ w[p + "router"].T, dim=-1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        order = sorted(range(experts), key=lambda e: (-float(scores[t, e]), e))[:top]
+        ranked = sorted(range(experts), key=lambda e: (-float(scores[t, e]), e))
+        order = ranked[:top]
+        if gaps is not None and top < experts:
+            gaps[t].append(float(1 - scores[t, ranked[top]] / scores[t, ranked[top - 1]]))
         total = sum(scores[t, e] for e in order) + 1e-20
         for e in order:
             out[t] += (scores[t, e] / total) * squared_relu_expert(h[t], w[f"{p}e{e}.up"], w[f"{p}e{e}.down"])
@@ -148,8 +153,9 @@ def layer_runs(config):
     return runs + [(i, None, False) for i in range(stop, n)]
 
 
-def forward(config, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one whole sequence (and, on request, the residual stream after every layer run)."""
+def forward(config, w, tokens, return_layers=False, gaps=None):
+    """Logits [T, vocab] of one whole sequence (and, on request, the residual stream after every layer run).
+    ``gaps``: a list of one list per token, filled with the routers' margins at that token."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(len(tokens))
     eps = config["norm"]["eps"]
@@ -169,7 +175,7 @@ def forward(config, w, tokens, return_layers=False):
         mlp = spec.get("mlp")
         if mlp is not None:
             delta = delta + (dense_feed_forward(h, w, p + "mlp.") if mlp["kind"] == "dense"
-                             else routed_feed_forward(h, w, p + "mlp.", mlp))
+                             else routed_feed_forward(h, w, p + "mlp.", mlp, gaps))
         x = x + delta
         if config.get("token_side"):
             x = token_side(x, tokens, w, layer, config["token_side"]["dim"], eps)

@@ -1,0 +1,432 @@
+"""The Zipedra design on the GPU against the plain implementation (tests/plain_zipedra.py): each mechanism alone,
+the residual stream layer by layer, whole prompts, token-by-token decoding, portions down to two tokens, mixed
+batches on a tight pool with four slots, long decoding, a far key, slots and pages used again, greedy generation
+through the engine's entry point, and the trace program."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_zipedra
+import replay_util
+from gpu_common import F32_ATOL, F32_RTOL, need_gpu, note_worst
+from zipedra_configs import CONFIGS, latent, lightning, moe
+
+pytestmark = pytest.mark.gpu
+CUDA = torch.device("cuda")
+# float32: every row is compared, with the bounds the Llama tests use.  A router whose last chosen score lies within
+# CLOSE (as a share of itself) of the next one may choose otherwise after rounding, which is no rounding error: such a
+# token's own row is left out.
+# bfloat16: rows kept in bfloat16 between kernels move a router's logits by up to a few per cent in the later layer
+# runs, so now and then a token is routed differently from the float64 model, and what it then leaves in keys and state
+# is read by every later token of its request.  The bound is therefore statistical: nine rows in ten within BF16_REL of
+# the sequence's largest logit (typical rows lie at a fifth of that), the median within a third of it.  A wrong key,
+# a lost state or a wrong page moves most rows of a request far beyond that, and float32 catches it on every row.
+CLOSE = {"float32": 1e-5, "bfloat16": 0.1}
+BF16_REL = 0.03
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from torchinferno_b200.weights.random_init import write_random_model
+    out = {}
+    for name, (config, seed) in CONFIGS.items():
+        out[name] = write_random_model(config, tmp_path_factory.mktemp(name), seed)
+    return out
+
+
+_plain: dict = {}
+
+
+def plain(folder, tokens, dtype):
+    """(logits [T, vocab], positions that a router's close call makes incomparable)."""
+    key = (str(folder), tuple(tokens))
+    if key not in _plain:
+        if str(folder) not in _plain:
+            _plain[str(folder)] = plain_zipedra.read_model_folder(folder)
+        config, weights = _plain[str(folder)]
+        gaps = [[] for _ in tokens]
+        _plain[key] = (plain_zipedra.forward(config, weights, tokens, gaps=gaps).numpy(), [min(g, default=1.0) for g in gaps])
+    logits, gaps = _plain[key]
+    return logits, {t for t, g in enumerate(gaps) if g < CLOSE[dtype]}
+
+
+def requests_for(config, seed, lengths):
+    g = torch.Generator().manual_seed(900 + seed)
+    return {f"q{i}": torch.randint(0, config["vocab"], (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+
+
+def compare(rows, folder, requests, dtype, what):
+    shares = []
+    for (name, pos), got_list in rows.items():
+        ref, close = plain(folder, requests[name], dtype)
+        if pos in close:
+            continue
+        for got in got_list:
+            got = np.asarray(got, dtype=np.float64)
+            assert np.isfinite(got).all(), f"{name}@{pos}: non-finite logits"
+            err = np.abs(got - ref[pos]).max()
+            if dtype == "float32":
+                bound = F32_ATOL + F32_RTOL * np.abs(ref[pos]).max()
+                assert err <= bound, f"{what}: {name}@{pos} ({dtype}): max error {err:.3e} exceeds {bound:.3e}"
+            else:
+                bound = BF16_REL * np.abs(ref).max()
+            shares.append(err / bound)
+    assert len(shares) >= max(1, len(rows) // 3), f"{what}: only {len(shares)} of {len(rows)} rows could be compared"
+    shares = np.sort(np.asarray(shares))
+    if dtype == "float32":
+        note_worst(f"zipedra {what} [{dtype}]", shares[-1])
+    else:
+        ninth, median = shares[int(0.9 * (len(shares) - 1))], shares[len(shares) // 2]
+        assert ninth <= 1.0 and median <= 1 / 3, f"{what} ({dtype}): nine in ten rows within {ninth:.2f} of the bound, median {median:.2f}"
+        note_worst(f"zipedra {what}, nine rows in ten [{dtype}]", ninth)
+
+
+def make_runner(folder, dtype, max_tokens, page_size=16, max_requests=4):
+    from torchinferno_b200.engine.factory import load_model, make_runner as make
+    model = load_model(folder, dtype=dtype)
+    return make(model, page_size=page_size, max_tokens=max_tokens + page_size * max_requests, max_requests=max_requests)
+
+
+def run_steps(runner, steps):
+    from torchinferno_b200.engine.batch import StepEntry
+    out = {}
+    with torch.inference_mode():
+        for step in steps:
+            logits = runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in step["entries"]])
+            if logits.shape[0]:
+                out[step["step"]] = logits.cpu().numpy()
+            runner.end(step["end"])
+            runner.cache.audit()
+    return out
+
+
+# ------------------------------------------------------------ whole models
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_the_residual_stream_after_every_layer_run(name, folders):
+    need_gpu()
+    from torchinferno_b200.engine.batch import StepEntry
+    from torchinferno_b200.parts.parallel_block import ParallelBlock
+    config, seed = CONFIGS[name]
+    tokens = requests_for(config, seed, [45])["q0"]
+    cfg, w = plain_zipedra.read_model_folder(folders[name])
+    _, want = plain_zipedra.forward(cfg, w, tokens, return_layers=True)
+    runner = make_runner(folders[name], "float32", 64)
+    seen, original = [], ParallelBlock.forward
+
+    def recording(self, stream, ctx):
+        original(self, stream, ctx)
+        seen.append(stream.residual.clone())
+    ParallelBlock.forward = recording
+    try:
+        with torch.inference_mode():
+            runner.step([StepEntry("a", tokens, [0])])
+    finally:
+        ParallelBlock.forward = original
+    assert len(seen) == want.shape[0]
+    for i, got in enumerate(seen):
+        err = (got.cpu().double() - want[i]).abs().max()
+        assert err <= 1e-4 * want[i].abs().max(), f"layer run {i}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_whole_tail_portions_and_mixed_batches(name, dtype, folders):
+    need_gpu()
+    config, seed = CONFIGS[name]
+    requests = requests_for(config, seed, [1, 2, 37, 70, 131, 64, 33])
+    page = {"ZA": 16, "ZB": 4, "ZC": 8}[name]
+    for kind, (steps, index) in {
+            "whole": replay_util.trace_whole(requests), "tail": replay_util.trace_tail_decode(requests, tail=40),
+            "portions": replay_util.trace_portions(requests, sizes=(2, 7, 16, 3, 33, 2, 5, 31, 32, 2, 64)),
+            "mixed": replay_util.trace_mixed(requests, seed=seed)}.items():
+        runner = make_runner(folders[name], dtype, replay_util.peak_tokens(steps), page_size=page)
+        rows = replay_util.gather(run_steps(runner, steps), index)
+        compare(rows, folders[name], requests, dtype, f"{name} {kind}")
+        assert not runner.cache.live_requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_every_token_decoded_alone_from_the_first_and_long_decoding(dtype, folders):
+    need_gpu()
+    config, seed = CONFIGS["ZA"]
+    requests = requests_for(config, seed + 5, [150, 9])
+    steps, index = replay_util.trace_tail_decode(requests, tail=10 ** 6)       # one token a step from position 0
+    runner = make_runner(folders["ZA"], dtype, replay_util.peak_tokens(steps), page_size=4)
+    rows = replay_util.gather(run_steps(runner, steps), index)
+    assert runner.counters["graph_steps"] > 100                              # the captured decode pass ran them
+    compare(rows, folders["ZA"], requests, dtype, "ZA token by token")
+
+
+def test_a_batch_of_unequal_requests_gives_each_what_it_gets_alone(folders):
+    need_gpu()
+    from torchinferno_b200.engine.batch import StepEntry
+    config, seed = CONFIGS["ZA"]
+    reqs = requests_for(config, seed + 9, [50, 3, 19, 1])
+    runner = make_runner(folders["ZA"], "float32", 4 * 64, page_size=8)
+    with torch.inference_mode():
+        alone = {}
+        for k, toks in reqs.items():
+            alone[k] = runner.step([StepEntry(k + "a", toks, list(range(len(toks))))]).cpu()
+            runner.end([k + "a"])
+        # together: a portion of each, then the rest of each, in another order (slots and pages are used again)
+        first = {k: max(1, len(t) // 2) for k, t in reqs.items()}
+        got = {k: [] for k in reqs}
+        out = runner.step([StepEntry(k, reqs[k][:first[k]], list(range(first[k]))) for k in reqs]).cpu()
+        row = 0
+        for k in reqs:
+            got[k].append(out[row:row + first[k]]); row += first[k]
+        rest = [k for k in reversed(list(reqs)) if len(reqs[k]) > first[k]]
+        out = runner.step([StepEntry(k, reqs[k][first[k]:], list(range(len(reqs[k]) - first[k]))) for k in rest]).cpu()
+        row = 0
+        for k in rest:
+            n = len(reqs[k]) - first[k]
+            got[k].append(out[row:row + n]); row += n
+        runner.end(list(reqs))
+    for k in reqs:
+        assert torch.allclose(torch.cat(got[k]), alone[k], atol=2e-6, rtol=2e-5), k
+
+
+# ------------------------------------------------------- mechanisms alone
+def _entries_batch(entries):
+    from torchinferno_b200.engine.batch import EntryPlacement, build_batch
+    places, row = [], 0
+    for rid, slot, start, n in entries:
+        places.append(EntryPlacement(rid, slot, row, n, start))
+        row += n
+    batch, _ = build_batch(places, [[0] * p.q_len for p in places], [[] for _ in places], [], CUDA)
+    return batch
+
+
+def _random_weights(part, seed, dtype):
+    from torchinferno_b200.weights.random_init import random_tensor
+    stored = {ws.name: random_tensor(ws, seed, dtype=torch.bfloat16) for ws in part.weight_specs()}
+    for ws in part.weight_specs():
+        if ws.role == "vector":
+            stored[ws.name] = (stored[ws.name].float() * (1 + 0.2 * torch.randn(ws.shape))).to(torch.bfloat16)
+    part.bind({k: (v.float() if dtype == torch.float32 or part_vector(part, k) else v).cuda() for k, v in stored.items()})
+    return {k: v.double() for k, v in stored.items()}
+
+
+def part_vector(part, name):
+    return any(ws.name == name and ws.role == "vector" for ws in part.weight_specs())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_attention_alone_in_portions_over_its_state(dtype):
+    """Portions that end just before, at and just after the kernel's chunk of 32 tokens; a head that forgets nothing
+    (decay 1) whose first token is made huge, so that it must still show two hundred tokens later; two requests in one
+    step; a slot used again starts from zero."""
+    need_gpu()
+    from torchinferno_b200.cache.manager import CacheManager
+    from torchinferno_b200.parts.base import LayerContext, PartSpec, build_part
+    W, m = 48, lightning(3, 16, 24, [1.0, 0.93, 0.4])
+    mixer = build_part("mixer", PartSpec("decay_linear_attention", {
+        "hidden_size": W, "heads": 3, "key_dim": 16, "value_dim": 24, "decay": m["decay"], "eps": 1e-6}), dtype=dtype, device=CUDA)
+    w = {"mix." + k: v for k, v in _random_weights(mixer, 4, dtype).items()}
+    cache = CacheManager([], [mixer.state_spec()], page_size=4, num_pages=4, max_requests=2, max_request_tokens=10 ** 6,
+                         dtype=dtype, device=CUDA)
+    x = torch.randn(230, W).to(dtype)
+    x[0] *= 6
+    other = torch.randn(40, W).to(dtype)
+    want = plain_zipedra.lightning_mixer(x.double(), w, "mix.", m, 1e-6)
+    want_other = plain_zipedra.lightning_mixer(other.double(), w, "mix.", m, 1e-6)
+    # the first token still counts at the end (the plain result changes when it is left out)
+    assert (plain_zipedra.lightning_mixer(x.double()[1:], w, "mix.", m, 1e-6)[-1] - want[-1]).abs().max() > 0.02 * want[-1].abs().max()
+    cache.open("warm"), cache.close("warm")
+    slot_r, slot_o = cache.open("r"), cache.open("o")
+    cache.states[0][slot_r].fill_(0.0)
+    outs, outs_other, pos, opos = [], [], 0, 0
+    for n, k in ((31, 0), (1, 7), (2, 0), (32, 1), (33, 0), (1, 32), (64, 0), (1, 0), (1, 0), (64, 0)):
+        entries = [("r", slot_r, pos, n)] + ([("o", slot_o, opos, k)] if k else [])
+        rows = torch.cat([x[pos:pos + n]] + ([other[opos:opos + k]] if k else [])).cuda().contiguous()
+        out = mixer.forward(rows, LayerContext(batch=_entries_batch(entries), state=cache.states[0]))
+        outs.append(out[:n]), outs_other.append(out[n:])
+        pos, opos = pos + n, opos + k
+    got, got_other = torch.cat(outs).cpu().double(), torch.cat(outs_other).cpu().double()
+    tol = 2e-5 if dtype == torch.float32 else BF16_REL
+    assert (got - want).abs().max() <= tol * want.abs().max()
+    assert (got_other - want_other[:opos]).abs().max() <= tol * want_other.abs().max()
+    # the slot of "o" goes to a new request: nothing of the old state is left
+    cache.close("o")
+    assert cache.open("n") == slot_o
+    out = mixer.forward(other[:5].cuda().contiguous(), LayerContext(batch=_entries_batch([("n", slot_o, 0, 5)]), state=cache.states[0]))
+    assert (out.cpu().double() - want_other[:5]).abs().max() <= tol * want_other.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_latent_attention_alone_with_a_far_key_at_a_page_border(dtype):
+    """A prompt of 300 tokens in portions, then single tokens, over pages of 8.  Token 7 (the last of the first page) and
+    the last tokens are scaled so that the late queries give that one far key nearly all their weight: an
+    attention that loses it (or reads the wrong page) is far off."""
+    need_gpu()
+    from torchinferno_b200.cache.manager import CacheManager
+    from torchinferno_b200.kernels import ops
+    from torchinferno_b200.parts.base import KVBinding, LayerContext, PartSpec, build_part
+    W, m = 64, latent(3, 16, 8, 24, 40, 0.25, base=1000.0, rot_dims=6)
+    mixer = build_part("mixer", PartSpec("latent_attention", {
+        "hidden_size": W, "heads": 3, "dim": 16, "rot_dim": 8, "value_dim": 24, "kv_rank": 40, "scale": 0.25,
+        "rot_base": 1000.0, "rot_dims": 6, "eps": 1e-6}), dtype=dtype, device=CUDA)
+    w = {"mix." + k: v for k, v in _random_weights(mixer, 8, dtype).items()}
+    T, far = 306, 7
+    x = torch.randn(T, W).to(dtype)
+    pos = torch.arange(T)
+    # The last six rows are nearly one vector, six times the usual size.  The far token's row is chosen so that its
+    # latent lies exactly along what head 0 of those queries looks for (W_uk_0^T q_0).  Both are kept out of the
+    # rotated key part (projected off W_dkv's last rows), or the late tokens' large rotated parts, at neighbouring
+    # positions, could outweigh everything else by chance.
+    rot_rows = w["mix.dkv"][40:]
+    base = torch.randn(W).double()
+    base = base - torch.linalg.pinv(rot_rows) @ (rot_rows @ base)
+    x[-6:] = (6 * (base[None] + 0.05 * torch.randn(6, W))).to(dtype)
+    looked_for = w["mix.uk"].view(3, 16, 40)[0].T @ (base @ w["mix.q"].T).view(3, 24)[0, :16]
+    direction = torch.linalg.pinv(w["mix.dkv"]) @ torch.cat([looked_for / w["mix.dkv.norm"], torch.zeros(8, dtype=torch.float64)])
+    x[far] = (direction / direction.norm() * W ** 0.5 * 3).to(dtype)
+    want = plain_zipedra.latent_attention_mixer(x.double(), w, "mix.", m, 1e-6, pos)
+    without = plain_zipedra.latent_attention_mixer(torch.cat([x[:far], x[far + 1:]]).double(), w, "mix.", m, 1e-6,
+                                                   torch.cat([pos[:far], pos[far + 1:]]))
+    assert (without[-1] - want[-1]).abs().max() > 0.15 * want[-1].abs().max()      # losing the far key shows
+    cache = CacheManager([mixer.cache_spec()], [None], page_size=8, num_pages=45, max_requests=3, max_request_tokens=320,
+                         dtype=dtype, device=CUDA)
+    cache.groups[0].pool.fill_(float("nan"))
+    cache.open("warm"), cache.extend("warm", 11)
+    cache.open("r")
+    outs, at = [], 0
+    for n in (3, 5, 2, 120, 17, 153) + (1,) * 6:
+        start = cache.extend("r", n)
+        for group, (idx, val) in zip(cache.groups, cache.drain_table_updates()):
+            if idx:
+                ops.scatter_i32(group.table_device, torch.tensor(idx, dtype=torch.int32).cuda(), torch.tensor(val, dtype=torch.int32).cuda())
+        b = cache.kv_binding(0)
+        ctx = LayerContext(batch=_entries_batch([("r", cache.slot("r"), start, n)]), error_word=cache.error_word,
+                           kv=KVBinding(b.pool, b.block_table, b.page_size, b.window, True, b.keys, b.values))
+        outs.append(mixer.forward(x[at:at + n].cuda().contiguous(), ctx))
+        at += n
+    assert at == T and int(cache.error_word) == 0
+    got = torch.cat(outs).cpu().double()
+    tol = 2e-5 if dtype == torch.float32 else BF16_REL
+    assert (got - want).abs().max() <= tol * want.abs().max(), (got - want).abs().max() / want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,top,shared,tokens", [(5, 2, 24, 300), (3, 3, 0, 70), (9, 1, 16, 3), (40, 4, 0, 200)])
+def test_routed_experts_alone(dtype, experts, top, shared, tokens):
+    need_gpu()
+    from torchinferno_b200.parts.base import LayerContext, PartSpec, build_part
+    W, ff = 40, 24
+    part = build_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": W, "experts": experts, "top": top, "expert_size": ff, "norm_eps": 1e-20, "shared_size": shared,
+        "shared_gate": bool(shared)}), dtype=dtype, device=CUDA)
+    w = {"mlp." + k: v for k, v in _random_weights(part, experts, dtype).items()}
+    x = torch.randn(tokens, W).to(dtype)
+    mlp = moe(experts, top, ff, shared or None)
+    gaps = [[] for _ in range(tokens)]
+    want = plain_zipedra.routed_feed_forward(x.double(), w, "mlp.", mlp, gaps)
+    got = part.forward(x.cuda().contiguous(), LayerContext(batch=None)).cpu().double()
+    clear = torch.tensor([min(g, default=1.0) >= (1e-5 if dtype == torch.float32 else 0.02) for g in gaps])
+    assert clear.sum() >= tokens // 3
+    tol = 2e-5 if dtype == torch.float32 else BF16_REL
+    assert (got - want)[clear].abs().max() <= tol * want.abs().max()
+    if top < experts:       # the tokens really go to different experts
+        scores = torch.softmax(x.double() @ w["mlp.router"].T, -1)
+        assert len(set(scores.argmax(-1).tolist())) > 1
+
+
+# ------------------------------------------------ entry point and programs
+def test_greedy_generation_through_the_engine_and_its_scheduler(folders):
+    need_gpu()
+    from torchinferno_b200.config.engine_config import EngineConfig
+    from torchinferno_b200.engine.engine import InferenceEngine
+    from torchinferno_b200.engine.types import GenerateRequest, SamplingConfig
+    config, seed = CONFIGS["ZA"]
+    cfg, w = plain_zipedra.read_model_folder(folders["ZA"])
+    prompts = list(requests_for(config, seed + 2, [5, 41, 1, 18, 66]).values())
+    new = 12
+    for dtype in ("float32", "bfloat16"):
+        with InferenceEngine.from_config(EngineConfig(model=str(folders["ZA"]), dtype=dtype, page_size=8, max_batch_size=3,
+                                                      prefill_chunk_size=16, max_num_batched_tokens=48, kv_cache_tokens=512)) as engine:
+            outs = engine.generate_many([GenerateRequest(f"g{i}", prompt_token_ids=p, sampling=SamplingConfig(new))
+                                         for i, p in enumerate(prompts)])
+        for prompt, out in zip(prompts, outs):
+            tokens = list(out.token_ids)
+            assert len(tokens) == new
+            logits = plain_zipedra.forward(cfg, w, (prompt + tokens)[:-1])
+            for i, tok in enumerate(tokens):
+                row = logits[len(prompt) + i - 1]
+                best = row.topk(2)
+                if dtype == "float32" and float(best.values[0] - best.values[1]) > 1e-4 * float(row.abs().max()):
+                    assert tok == int(best.indices[0])
+                else:
+                    assert tok in best.indices.tolist()
+
+
+def test_the_trace_program_replays_a_zipedra_folder(folders, tmp_path):
+    need_gpu()
+    config, seed = CONFIGS["ZB"]
+    requests = requests_for(config, seed + 3, [30, 75, 2])
+    steps, index = replay_util.trace_mixed(requests, seed=3)
+    out_dir = tmp_path / "out"
+    import subprocess
+    import sys
+    cmd = [sys.executable, str(replay_util.ROOT / "bin" / "trace_run"), "--model", str(folders["ZB"]), "--dtype", "float32",
+           "--out", str(out_dir), "--max-tokens", str(replay_util.peak_tokens(steps))]
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    try:
+        for step in steps:
+            proc.stdin.write(json.dumps(step) + "\n")
+            proc.stdin.flush()
+            assert proc.stdout.readline().strip() == f"done {step['step']}"
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    results = {}
+    for step in steps:
+        wanted = sum(len(e["want"]) for e in step["entries"])
+        if wanted:
+            results[step["step"]] = np.fromfile(out_dir / f"{step['step']}.f32", dtype="<f4").reshape(wanted, config["vocab"])
+    compare(replay_util.gather(results, index), folders["ZB"], requests, "float32", "ZB trace program")
+
+
+# ------------------------------------------------- the two attention kernels
+@pytest.mark.parametrize("heads,rank,rot,page", [(6, 128, 16, 16), (16, 512, 64, 16), (3, 64, 32, 8), (20, 192, 16, 32)])
+def test_latent_attention_kernels_agree_with_plain_arithmetic(heads, rank, rot, page):
+    """The tensor-core kernel and the CUDA-core kernel on the same bf16 latent rows, against float64: a ragged step
+    (prompt portions that begin and end off the 64-key tile edges, beside single tokens) and a step of single tokens
+    with contexts just below, at and above tile and page edges (the split over the context and its merge)."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    width = rank + rot
+    g = torch.Generator().manual_seed(rank + heads)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=CUDA)
+    cases = {"ragged": [(0, 70), (63, 2), (64, 1), (100, 129), (5, 1)], "single": [(0, 1), (62, 1), (63, 1), (64, 1), (127, 1), (300, 1), (511, 1)]}
+    for name, entries in cases.items():
+        pages_per = max(-(-(start + n) // page) for start, n in entries)
+        total = len(entries) * pages_per
+        keys = (torch.randn(total, 1, page, width, generator=g) * 0.7).to(torch.bfloat16)
+        table = torch.randperm(total, generator=g).to(torch.int32).view(len(entries), pages_per)
+        n_tokens = sum(n for _, n in entries)
+        folded = torch.randn(n_tokens, heads, width, generator=g) * 0.3
+        q_start = [0]
+        for _, n in entries:
+            q_start.append(q_start[-1] + n)
+        want = torch.empty(n_tokens, heads, rank, dtype=torch.float64)
+        for e, (start, n) in enumerate(entries):
+            ctx = start + n
+            pos = torch.arange(ctx)
+            rows = keys[table[e][pos // page].long(), 0, pos % page].double()                  # [ctx, width]
+            q = folded[q_start[e]:q_start[e + 1]].to(torch.bfloat16).double()                    # the tensor-core kernel rounds q
+            scores = torch.einsum("thw,sw->ths", q, rows) * 0.11
+            hidden = pos[None, :] > (start + torch.arange(n))[:, None]
+            scores = scores.masked_fill(hidden[:, None, :], float("-inf"))
+            want[q_start[e]:q_start[e + 1]] = torch.einsum("ths,sc->thc", torch.softmax(scores, -1), rows[:, :rank])
+        args = (folded.cuda(), keys.cuda(), None, i32(q_start), i32([s for s, _ in entries]), i32(list(range(len(entries)))),
+                table.cuda().contiguous(), len(entries), max(n for _, n in entries), heads, rank, rot, 0.11)
+        max_kv = max(s + n for s, n in entries)
+        for simt in (False, True):
+            out = torch.empty(n_tokens, heads, rank, device=CUDA)
+            ops.latent_attention(*args[:2], out, *args[3:], max_kv_len=max_kv, force_simt=simt)
+            err = (out.cpu().double() - want).abs().max()
+            # (the CUDA-core kernel keeps q in fp32: its distance from a reference with rounded q is that rounding)
+            assert err <= (4e-3 if simt else 2e-4) * want.abs().max(), f"{name}, simt={simt}: {err:.3e}"

@@ -5,6 +5,9 @@
     python -m torchinferno_b200.bench_kernels gemm --rows 8
     python -m torchinferno_b200.bench_kernels elementwise --rows 2048
     python -m torchinferno_b200.bench_kernels step-timeline --layers 32 --batch 8 --context 3072
+    python -m torchinferno_b200.bench_kernels latent-attention --tokens 2048 --batch 8 --context 2048
+    python -m torchinferno_b200.bench_kernels linear-attention --tokens 2048 --batch 8
+    python -m torchinferno_b200.bench_kernels expert-product --tokens 2048
 
 Each run prints one JSON line per case: microseconds (median of CUDA-event timings, an L2 flush
 between iterations), the bytes or flops the kernel has to move or do, and the fraction of the
@@ -251,6 +254,81 @@ def run_step_timeline(args) -> None:
         end = e.time_range.end
 
 
+def run_latent_attention(args) -> None:
+    """The latent attention kernel on a prompt of --tokens (flops: folded scores over rank + rot and values over rank, causal)
+    and on --batch single tokens at --context (bytes: the latent rows of every context once)."""
+    h, c, r, page = args.heads, args.rank, args.rot, args.page_size
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    timer = Timer(args.iters)
+    for mode in ("prompt", "single tokens"):
+        n_entries, ctx = (1, args.tokens) if mode == "prompt" else (args.batch, args.context)
+        pages_per = -(-ctx // page)
+        keys = (torch.randn(n_entries * pages_per, 1, page, c + r, device="cuda") * 0.5).to(torch.bfloat16)
+        table = torch.randperm(n_entries * pages_per, device="cuda", dtype=torch.int32).view(n_entries, pages_per).contiguous()
+        n = ctx if mode == "prompt" else n_entries
+        folded = torch.randn(n, h, c + r, device="cuda") * 0.05
+        out = torch.empty(n, h, c, device="cuda")
+        if mode == "prompt":
+            q_start, kv_start, slots, max_q = i32([0, n]), i32([0]), i32([0]), n
+            flops, moved = 2 * h * (2 * c + r) * ctx * (ctx + 1) / 2, None
+        else:
+            q_start, kv_start, slots, max_q = i32(list(range(n + 1))), i32([ctx - 1] * n), i32(list(range(n))), 1
+            flops, moved = None, n * ctx * (c + r) * 2
+        fn = lambda: ops.latent_attention(folded, keys, out, q_start, kv_start, slots, table, n_entries, max_q, h, c, r, 0.07,
+                                          max_kv_len=ctx)
+        report(f"latent_attention[{mode}]", timer(fn), flops=flops, bytes_moved=moved, entries=n_entries, context=ctx, heads=h,
+               rank=c, rot=r)
+
+
+def run_linear_attention(args) -> None:
+    """The decayed linear attention kernel on a prompt of --tokens (flops of the chunked form) and on --batch single
+    tokens (bytes: every head's state read and written once)."""
+    h, d, v = args.heads, args.key_dim, args.value_dim
+    chunk = ops.linear_attention_chunk(d, v)
+    powers = (torch.full((h, 1), 0.99, dtype=torch.float64) ** torch.arange(chunk + 1, dtype=torch.float64)[None]).float().cuda()
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    timer = Timer(args.iters)
+    for mode in ("prompt", "single tokens"):
+        n_entries, n = (1, args.tokens) if mode == "prompt" else (args.batch, args.batch)
+        q, k = (torch.randn(n, h * d, device="cuda").to(torch.bfloat16) for _ in range(2))
+        val = torch.randn(n, h * v, device="cuda").to(torch.bfloat16)
+        out = torch.empty(n, h * v, device="cuda")
+        state = torch.zeros(n_entries, h, d, v, device="cuda")
+        q_start = i32([0, n]) if mode == "prompt" else i32(list(range(n + 1)))
+        slots = i32(list(range(n_entries)))
+        fn = lambda: ops.linear_attention(q, k, val, out, state, powers, q_start, slots, n_entries, h, d, v, silu=True)
+        if mode == "prompt":
+            flops = 2 * h * n * (chunk * (d + v) / 2 + 2 * d * v)
+            report("linear_attention[prompt]", timer(fn), flops=flops, tokens=n, heads=h, key_dim=d, value_dim=v, chunk=chunk)
+        else:
+            report("linear_attention[single tokens]", timer(fn), bytes_moved=2 * n * h * d * v * 4, batch=n, heads=h, key_dim=d,
+                   value_dim=v)
+
+
+def run_expert_product(args) -> None:
+    """Both products of the routed experts over --tokens * --top sorted rows, and beside them one dense product of the same
+    flops through the engine's ``linear`` (the like kernel of a dense feed-forward)."""
+    from torchinferno_b200.kernels.gemm import LinearWeight, linear
+    t, e, top, w, ff = args.tokens, args.experts, args.top, args.hidden, args.expert_size
+    x = torch.randn(t, w, device="cuda").to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(e, device="cuda")[:top] for _ in range(t)]).to(torch.int32).contiguous()
+    offsets = torch.empty(e + 1, dtype=torch.int32, device="cuda")
+    order, place = (torch.empty(t * top, dtype=torch.int32, device="cuda") for _ in range(2))
+    ops.moe_group(ids, e, offsets, order, place)
+    up = (torch.randn(e, ff, w, device="cuda") * 0.02).to(torch.bfloat16)
+    down = (torch.randn(e, w, ff, device="cuda") * 0.02).to(torch.bfloat16)
+    inner = torch.empty(t * top, ff, dtype=torch.bfloat16, device="cuda")
+    outer = torch.empty(t * top, w, dtype=torch.float32, device="cuda")
+    timer = Timer(args.iters)
+    flops = 2 * t * top * w * ff
+    report("expert_product[up, relu^2]", timer(lambda: ops.moe_expert_product(x, up, inner, offsets, order, top, x_by_pair=True, act="relu2")),
+           flops=flops, tokens=t, experts=e, top=top, hidden=w, expert_size=ff)
+    report("expert_product[down]", timer(lambda: ops.moe_expert_product(inner, down, outer, offsets, order, top, x_by_pair=False)),
+           flops=flops, tokens=t, experts=e, top=top, hidden=w, expert_size=ff)
+    dense = LinearWeight((torch.randn(top * ff, w, device="cuda") * 0.02).to(torch.bfloat16), few_rows_tcgen05=False)
+    report("linear[dense, the same flops]", timer(lambda: linear(x, dense)), flops=flops, tokens=t, hidden=w, out=top * ff)
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m torchinferno_b200.bench_kernels", description=__doc__.splitlines()[0])
     parser.add_argument("--ordinary-launches", action="store_true",
@@ -301,6 +379,32 @@ def main(argv=None) -> int:
     p.add_argument("--prompt", action="store_true", help="the step of one whole prompt of --context tokens instead of a decode step")
     common(p)
     p.set_defaults(func=run_step_timeline, iters=3)
+    p = sub.add_parser("latent-attention")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--rank", type=int, default=512)
+    p.add_argument("--rot", type=int, default=64)
+    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_latent_attention)
+    p = sub.add_parser("linear-attention")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--key-dim", type=int, default=128)
+    p.add_argument("--value-dim", type=int, default=128)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_linear_attention)
+    p = sub.add_parser("expert-product")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--experts", type=int, default=32)
+    p.add_argument("--top", type=int, default=4)
+    p.add_argument("--hidden", type=int, default=2048)
+    p.add_argument("--expert-size", type=int, default=1024)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_expert_product)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels needs a CUDA device")

@@ -63,6 +63,7 @@ def unregister_architecture(name: str) -> None:
 
 
 def registered_architectures() -> tuple[str, ...]:
+    _ensure_builtin()
     return tuple(sorted({entry.name for entry in _BY_ARCHITECTURE.values()}))
 
 

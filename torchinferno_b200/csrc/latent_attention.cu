@@ -11,11 +11,16 @@
 //                     page; qr_j = rotate(q_j[dim:]) written behind a_j in the folded query rows.  Rotary pairs
 //                     are (2i, 2i+1), angle = position * inv_freq[i] in fp32, on the first 2 * n_freq elements.
 //   latent_attention  causal softmax attention of the folded queries [tokens, heads, rank + rot] (fp32) over
-//                     the paged latent rows; out [tokens, heads, rank] (fp32).  CUDA cores, fp32 throughout:
-//                     one warp owns one (token, head) row and walks the keys in blocks of 32 aligned to absolute
-//                     positions, so a row's arithmetic does not depend on how the batch was cut.
-#include "common.cuh"
-#include <math_constants.h>
+//                     the paged latent rows; out [tokens, heads, rank] (fp32).  Two kernels:
+//                     - CUDA cores, fp32 throughout (the 32-bit path, and every shape): one warp owns one
+//                       (token, head) row and walks the keys in blocks of 32 aligned to absolute positions, so a
+//                       row's arithmetic does not depend on how the batch was cut;
+//                     - tensor cores (mma.sync m16n8k16) for bf16 latent rows with rank a multiple of 64: tiles of
+//                       64 keys aligned to absolute positions through two cp.async stages; the four warps of a
+//                       block split a tile's keys for the scores and the value columns for the output; scores,
+//                       maxima, sums and the accumulator are fp32, and the softmax weights enter the second
+//                       product as TWO bf16 terms (p = hi + lo, 16 bits of mantissa), so they are not cut to 8.
+#include "mma.cuh"
 
 namespace tib {
 
@@ -106,6 +111,11 @@ struct LatentAttnArgs {
   float scale;
   int head_chunk, q_tile;
   int* error_word;
+  // a step of single tokens may cut every context into `n_splits` runs of `blocks_per_split` key blocks, one block
+  // each: they leave their running maximum, sum and unnormalised output in `partial` [tokens, heads, n_splits,
+  // 2 + rank] and latent_merge_kernel puts them together
+  float* partial;
+  int n_splits, blocks_per_split;
 };
 
 template <typename T, int DPL>
@@ -123,7 +133,8 @@ latent_attention_kernel(const float* __restrict__ folded, const T* __restrict__ 
   const int hc = min(a.head_chunk, a.heads - h0);
   const int row0 = a.q_start[entry];
   const int q_len = a.q_start[entry + 1] - row0;
-  const int t0 = blockIdx.x * a.q_tile;
+  const int split = a.partial ? blockIdx.x : 0;
+  const int t0 = a.partial ? 0 : blockIdx.x * a.q_tile;
   if (t0 >= q_len) return;
   const int nt = min(a.q_tile, q_len - t0);
   const int nrows = nt * hc;
@@ -145,8 +156,12 @@ latent_attention_kernel(const float* __restrict__ folded, const T* __restrict__ 
 #pragma unroll
     for (int j = 0; j < DPL; ++j) acc[i][j] = 0.f;
   }
-  const int b_hi = last_pos / kLatKeys;
-  for (int b = 0; b <= b_hi; ++b) {
+  int b_lo = 0, b_hi = last_pos / kLatKeys;
+  if (a.partial) {
+    b_lo = split * a.blocks_per_split;
+    b_hi = min(b_hi, b_lo + a.blocks_per_split - 1);
+  }
+  for (int b = b_lo; b <= b_hi; ++b) {
     __syncthreads();
     // Latent rows of block b; rows past last_pos are not written yet (or are nobody's): zeros, always masked.
     for (int e = threadIdx.x; e < kLatKeys * w; e += blockDim.x) {
@@ -199,6 +214,16 @@ latent_attention_kernel(const float* __restrict__ folded, const T* __restrict__ 
     const int r = warp * kLatRowsPerWarp + i;
     if (r >= nrows) continue;
     const int t = r / hc, g = r - t * hc;
+    if (a.partial) {      // (one token per entry: t = 0)
+      float* p = a.partial + (((size_t)row0 * a.heads + h0 + g) * a.n_splits + split) * (2 + a.rank);
+      if (lane == 0) { p[0] = m[i]; p[1] = l[i]; }
+#pragma unroll
+      for (int j = 0; j < DPL; ++j) {
+        const int dd = lane + 32 * j;
+        if (dd < a.rank) p[2 + dd] = acc[i][j];
+      }
+      continue;
+    }
     float* dst = out + ((size_t)(row0 + t0 + t) * a.heads + h0 + g) * a.rank;
     const float inv = 1.f / l[i];
 #pragma unroll
@@ -207,6 +232,280 @@ latent_attention_kernel(const float* __restrict__ folded, const T* __restrict__ 
       if (dd < a.rank) dst[dd] = acc[i][j] * inv;
     }
   }
+}
+
+// grid (heads, tokens): out = sum_s w_s acc_s / sum_s w_s l_s with w_s = exp(m_s - max m); a run without keys has m = -inf
+__global__ void latent_merge_kernel(const float* __restrict__ partial, float* __restrict__ out, int heads, int n_splits, int rank) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = (size_t)blockIdx.y * heads + blockIdx.x;
+  const float* p = partial + row * n_splits * (2 + rank);
+  float mx = -CUDART_INF_F;
+  for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, p[(size_t)s * (2 + rank)]);
+  float total = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = p[(size_t)s * (2 + rank)];
+    if (ms != -CUDART_INF_F) total = fmaf(expf(ms - mx), p[(size_t)s * (2 + rank) + 1], total);
+  }
+  const float inv = 1.f / total;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = p[(size_t)s * (2 + rank)];
+      if (ms != -CUDART_INF_F) acc = fmaf(expf(ms - mx), p[(size_t)s * (2 + rank) + 2 + c], acc);
+    }
+    out[row * rank + c] = acc * inv;
+  }
+}
+
+// ------------------------------------------------------- tensor-core kernel
+constexpr int kMmaKeys = 64;        // keys per tile
+constexpr int kMmaWarps = 4;
+
+static inline size_t latent_mma_smem(int width, int mt) {
+  const size_t wp = width + 8;
+  return 2 * ((size_t)mt * 16 * wp + 2 * (size_t)kMmaKeys * wp + 2 * (size_t)mt * 16 * (kMmaKeys + 8))   // bf16: Q, K x 2, P hi / lo
+         + 4 * ((size_t)2 * kMmaWarps * mt * 16);                                                          // fp32: maxima and sums per warp
+}
+
+// MT: m-tiles of 16 rows a block owns (rows are (token, head) pairs of one entry, heads fastest);
+// R64 = rank / 64: every warp owns 16 * R64 value columns.
+template <int MT, int R64>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+latent_attention_mma_kernel(const float* __restrict__ folded, const __nv_bfloat16* __restrict__ pool, float* __restrict__ out,
+                            LatentAttnArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int RB = MT * 16;
+  const int w = a.width, wp = w + 8, pp = kMmaKeys + 8;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [RB][wp]
+  __nv_bfloat16* k_s = q_s + RB * wp;                                     // [2][64][wp]
+  __nv_bfloat16* p_hi = k_s + 2 * kMmaKeys * wp;                          // [RB][pp]
+  __nv_bfloat16* p_lo = p_hi + RB * pp;                                   // [RB][pp]
+  float* red_max = reinterpret_cast<float*>(p_lo + RB * pp);              // [4][RB]
+  float* red_sum = red_max + kMmaWarps * RB;                              // [4][RB]
+  pdl_wait();
+  pdl_trigger();
+  const int entry = blockIdx.y;
+  const int row0 = a.q_start[entry];
+  const int q_len = a.q_start[entry + 1] - row0;
+  const int total_rows = q_len * a.heads;
+  const int split = a.partial ? blockIdx.x : 0;
+  const int r0 = a.partial ? blockIdx.z * RB : blockIdx.x * RB;           // first (token, head) row of the block
+  if (r0 >= total_rows) return;
+  const int nrows = min(RB, total_rows - r0);
+  const int kv0 = a.kv_start[entry];
+  const int last_pos = kv0 + (r0 + nrows - 1) / a.heads;                  // highest key any row of the block reads
+  const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+
+  for (int e = tid; e < RB * w; e += blockDim.x) {
+    const int r = e / w, dd = e - r * w;
+    q_s[r * wp + dd] = __float2bfloat16_rn(r < nrows ? folded[((size_t)row0 * a.heads + r0 + r) * w + dd] : 0.f);
+  }
+  int tile_lo = 0, tile_hi = last_pos / kMmaKeys;
+  if (a.partial) {      // (blocks_per_split counts runs of 32 keys; a tile is two of them)
+    const int tiles_per_split = (a.blocks_per_split + 1) / 2;
+    tile_lo = split * tiles_per_split;
+    tile_hi = min(tile_hi, tile_lo + tiles_per_split - 1);
+  }
+  const int pieces_per_key = w / 8;
+  auto fetch = [&](int stage, int tile) {
+    __nv_bfloat16* dst = k_s + (size_t)stage * kMmaKeys * wp;
+    for (int e = tid; e < kMmaKeys * pieces_per_key; e += blockDim.x) {
+      const int j = e / pieces_per_key, c = (e - j * pieces_per_key) * 8;
+      const int kp = tile * kMmaKeys + j;
+      bool valid = kp <= last_pos;
+      const __nv_bfloat16* src = pool;
+      if (valid) {
+        const int page = table[kp / a.page_size];
+        if (page >= 0 && page < a.num_pages) {
+          src = pool + (size_t)page * a.page_stride + (size_t)(kp % a.page_size) * w + c;
+        } else {
+          valid = false;
+          if (a.error_word) atomicExch(a.error_word, 0x30000 + entry);
+        }
+      }
+      cp_async16(dst + j * wp + c, src, valid);      // (not valid: zeros; such keys are always masked)
+    }
+    cp_async_commit();
+  };
+
+  float m_run[MT][2], l_run[MT][2], o[MT][2 * R64][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    m_run[mt][0] = m_run[mt][1] = -CUDART_INF_F;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+#pragma unroll
+    for (int n = 0; n < 2 * R64; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[mt][n][c] = 0.f;
+  }
+  int qpos[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = mt * 16 + g + h * 8;
+      qpos[mt][h] = r < nrows ? kv0 + (r0 + r) / a.heads : -1;      // -1: no key is allowed
+    }
+
+  if (tile_lo <= tile_hi) fetch(0, tile_lo);
+  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
+    const int stage = (tile - tile_lo) & 1;
+    if (tile + 1 <= tile_hi) {
+      fetch(stage ^ 1, tile + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();                                   // the tile (and, the first time, q_s) is in shared memory
+    const __nv_bfloat16* kt = k_s + (size_t)stage * kMmaKeys * wp;
+    // scores of this warp's 16 keys
+    float s[MT][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[mt][n][c] = 0.f;
+    for (int kk = 0; kk < w; kk += 16) {
+      uint32_t b[4];
+      ldmatrix_x4(b, kt + (warp * 16 + ((lane >> 4) << 3) + (lane & 7)) * wp + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t qa[4];
+        ldmatrix_x4(qa, q_s + (mt * 16 + (lane & 15)) * wp + kk + (lane >> 4) * 8);
+        mma_bf16(s[mt][0], qa, b[0], b[1]);
+        mma_bf16(s[mt][1], qa, b[2], b[3]);
+      }
+    }
+    const int key0 = tile * kMmaKeys + warp * 16;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = -CUDART_INF_F;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int key = key0 + n * 8 + 2 * t4 + c;
+            float& v = s[mt][n][2 * h + c];
+            v = key <= qpos[mt][h] ? v * a.scale : -CUDART_INF_F;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        if (t4 == 0) red_max[warp * RB + mt * 16 + g + h * 8] = mx;
+      }
+    __syncthreads();
+    float alpha[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = mt * 16 + g + h * 8;
+        float mx = fmaxf(fmaxf(red_max[r], red_max[RB + r]), fmaxf(red_max[2 * RB + r], red_max[3 * RB + r]));
+        const float m_new = fmaxf(m_run[mt][h], mx);
+        const float base = m_new == -CUDART_INF_F ? 0.f : m_new;
+        alpha[mt][h] = m_run[mt][h] == -CUDART_INF_F ? 0.f : expf(m_run[mt][h] - base);
+        m_run[mt][h] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const float p0 = expf(s[mt][n][2 * h] - base), p1 = expf(s[mt][n][2 * h + 1] - base);
+          sum += p0 + p1;
+          const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
+          const int col = warp * 16 + n * 8 + 2 * t4;
+          *reinterpret_cast<__nv_bfloat162*>(p_hi + r * pp + col) = __halves2bfloat162(h0, h1);
+          *reinterpret_cast<__nv_bfloat162*>(p_lo + r * pp + col) =
+              __floats2bfloat162_rn(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (t4 == 0) red_sum[warp * RB + r] = sum;
+      }
+    __syncthreads();
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = mt * 16 + g + h * 8;
+        l_run[mt][h] = l_run[mt][h] * alpha[mt][h] + (red_sum[r] + red_sum[RB + r]) + (red_sum[2 * RB + r] + red_sum[3 * RB + r]);
+#pragma unroll
+        for (int n = 0; n < 2 * R64; ++n) {
+          o[mt][n][2 * h] *= alpha[mt][h];
+          o[mt][n][2 * h + 1] *= alpha[mt][h];
+        }
+      }
+    // output columns of this warp: [warp * 16 * R64, +16 * R64) of the tile's rows read as values
+    const int col0 = warp * 16 * R64;
+#pragma unroll
+    for (int ks = 0; ks < kMmaKeys / 16; ++ks) {
+      uint32_t ph[MT][4], pl[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        ldmatrix_x4(ph[mt], p_hi + (mt * 16 + (lane & 15)) * pp + ks * 16 + (lane >> 4) * 8);
+        ldmatrix_x4(pl[mt], p_lo + (mt * 16 + (lane & 15)) * pp + ks * 16 + (lane >> 4) * 8);
+      }
+#pragma unroll
+      for (int cg = 0; cg < R64; ++cg) {
+        uint32_t v[4];     // (k lo, n 0-7), (k hi, n 0-7), (k lo, n 8-15), (k hi, n 8-15), transposed on the way in
+        ldmatrix_x4_trans(v, kt + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * wp + col0 + cg * 16 + ((lane >> 4) << 3));
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(o[mt][2 * cg], ph[mt], v[0], v[1]);
+          mma_bf16(o[mt][2 * cg], pl[mt], v[0], v[1]);
+          mma_bf16(o[mt][2 * cg + 1], ph[mt], v[2], v[3]);
+          mma_bf16(o[mt][2 * cg + 1], pl[mt], v[2], v[3]);
+        }
+      }
+    }
+    __syncthreads();      // the stage, p_hi / p_lo and the reduction arrays are free again
+  }
+
+  const int col0 = warp * 16 * R64;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = mt * 16 + g + h * 8;
+      if (r >= nrows) continue;
+      if (a.partial) {      // (one token per entry: the block's rows are heads)
+        float* p = a.partial + (((size_t)row0 * a.heads + r0 + r) * a.n_splits + split) * (2 + a.rank);
+        if (warp == 0 && t4 == 0) { p[0] = m_run[mt][h]; p[1] = l_run[mt][h]; }
+#pragma unroll
+        for (int n = 0; n < 2 * R64; ++n) {
+          p[2 + col0 + n * 8 + 2 * t4] = o[mt][n][2 * h];
+          p[2 + col0 + n * 8 + 2 * t4 + 1] = o[mt][n][2 * h + 1];
+        }
+      } else {
+        float* dst = out + ((size_t)row0 * a.heads + r0 + r) * a.rank;
+        const float inv = 1.f / l_run[mt][h];
+#pragma unroll
+        for (int n = 0; n < 2 * R64; ++n) {
+          dst[col0 + n * 8 + 2 * t4] = o[mt][n][2 * h] * inv;
+          dst[col0 + n * 8 + 2 * t4 + 1] = o[mt][n][2 * h + 1] * inv;
+        }
+      }
+    }
+}
+
+template <int MT, int R64>
+static int launch_latent_mma(const float* folded, const void* pool, float* out, const LatentAttnArgs& a, int n_entries,
+                             int max_q_len, cudaStream_t stream) {
+  const size_t smem = latent_mma_smem(a.width, MT);
+  if (smem > 227 * 1024) return TIB_E_SMEM;
+  auto kern = latent_attention_mma_kernel<MT, R64>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int rb = MT * 16;
+  dim3 grid(a.partial ? a.n_splits : ceil_div(max_q_len * a.heads, rb), n_entries, a.partial ? ceil_div(a.heads, rb) : 1);
+  TIB_LAUNCH_DEPENDENT(kern, grid, kMmaWarps * 32, smem, stream, folded, (const __nv_bfloat16*)pool, out, a);
+  if (a.partial)
+    TIB_LAUNCH_DEPENDENT(latent_merge_kernel, dim3(a.heads, n_entries), 128, 0, stream, (const float*)a.partial, out, a.heads,
+                         a.n_splits, a.rank);
+  return TIB_OK;
 }
 
 template <typename T, int DPL>
@@ -219,8 +518,11 @@ static int launch_latent_attention(const float* folded, const void* pool, float*
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(ceil_div(max_q_len, a.q_tile), n_entries, ceil_div(a.heads, a.head_chunk));
+  dim3 grid(a.partial ? a.n_splits : ceil_div(max_q_len, a.q_tile), n_entries, ceil_div(a.heads, a.head_chunk));
   TIB_LAUNCH_DEPENDENT(kern, grid, kLatWarps * 32, smem, stream, folded, (const T*)pool, out, a);
+  if (a.partial)
+    TIB_LAUNCH_DEPENDENT(latent_merge_kernel, dim3(a.heads, n_entries), 128, 0, stream, (const float*)a.partial, out, a.heads,
+                         a.n_splits, a.rank);
   return TIB_OK;
 }
 
@@ -256,11 +558,25 @@ TIB_API int tib_latent_append(const void* dkv, int64_t ld_dkv, const void* q, in
   return TIB_OK;
 }
 
+// How many runs a step of `n_entries` single tokens should cut its contexts of up to `max_kv_len` keys into (1: none).
+TIB_API int tib_latent_attention_splits(int n_entries, int heads, int max_kv_len) {
+  const int head_chunk = heads < kLatRows ? heads : kLatRows;
+  const int blocks = n_entries * ceil_div(heads, head_chunk);
+  const int key_blocks = ceil_div(max_kv_len, kLatKeys);
+  int splits = (2 * 148) / (blocks < 1 ? 1 : blocks);
+  if (splits > key_blocks) splits = key_blocks;
+  if (splits > 64) splits = 64;
+  return splits < 1 ? 1 : splits;
+}
+
 // folded: [tokens, heads, rank + rot] fp32; pool: pages of [page_size][rank + rot] in `dtype`; out: [tokens, heads, rank] fp32.
+// n_splits > 1 (a step of single tokens only, contexts of at most max_kv_len keys): partial [tokens, heads, n_splits, 2 + rank].
+// force_simt: the CUDA-core kernel also where the tensor-core one takes the shape.
 TIB_API int tib_latent_attention(const float* folded, const void* pool, float* out, const int* q_start, const int* kv_start,
                                  const int* slots, const int* block_table, int table_stride, int n_entries, int max_q_len,
                                  int heads, int rank, int rot, int page_size, int64_t page_stride, int num_pages, float scale,
-                                 int* error_word, int dtype, cudaStream_t stream) {
+                                 float* partial, int n_splits, int max_kv_len, int force_simt, int* error_word, int dtype,
+                                 cudaStream_t stream) {
   if (n_entries == 0 || max_q_len == 0) return TIB_OK;
   if (!folded || !pool || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
   if (heads < 1 || rank < 1 || rot < 0 || page_size < 1 || rank > 512 || n_entries > 65535) return TIB_E_SIZE;
@@ -268,9 +584,31 @@ TIB_API int tib_latent_attention(const float* folded, const void* pool, float* o
   a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table; a.table_stride = table_stride;
   a.heads = heads; a.rank = rank; a.width = rank + rot; a.page_size = page_size; a.num_pages = num_pages;
   a.page_stride = page_stride; a.scale = scale; a.error_word = error_word;
+  a.partial = nullptr; a.n_splits = 1; a.blocks_per_split = 0;
+  if (n_splits > 1) {
+    if (!partial || max_q_len != 1 || max_kv_len < 1) return TIB_E_ARG;
+    a.partial = partial; a.n_splits = n_splits;
+    a.blocks_per_split = ceil_div(ceil_div(max_kv_len, kLatKeys), n_splits);
+  }
   a.head_chunk = heads < kLatRows ? heads : kLatRows;
   a.q_tile = kLatRows / a.head_chunk;
   if (ceil_div(heads, a.head_chunk) > 65535) return TIB_E_SIZE;
+  const int width = rank + rot;
+  if (dtype == TIB_BF16 && !force_simt && width % 16 == 0 && rank % 64 == 0 && (page_stride % 8) == 0 && ((uintptr_t)pool & 15) == 0) {
+    const int r64 = rank / 64;
+    const bool single = max_q_len == 1;
+    if (latent_mma_smem(width, single ? 1 : 2) <= 227 * 1024 && (r64 <= 4 || r64 == 6 || r64 == 8)) {
+#define TIB_LAT_MMA(MT)                                                                                         \
+  (r64 == 1 ? launch_latent_mma<MT, 1>(folded, pool, out, a, n_entries, max_q_len, stream)                     \
+   : r64 == 2 ? launch_latent_mma<MT, 2>(folded, pool, out, a, n_entries, max_q_len, stream)                   \
+   : r64 == 3 ? launch_latent_mma<MT, 3>(folded, pool, out, a, n_entries, max_q_len, stream)                   \
+   : r64 == 4 ? launch_latent_mma<MT, 4>(folded, pool, out, a, n_entries, max_q_len, stream)                   \
+   : r64 == 6 ? launch_latent_mma<MT, 6>(folded, pool, out, a, n_entries, max_q_len, stream)                   \
+              : launch_latent_mma<MT, 8>(folded, pool, out, a, n_entries, max_q_len, stream))
+      return single ? TIB_LAT_MMA(1) : TIB_LAT_MMA(2);
+#undef TIB_LAT_MMA
+    }
+  }
   const int dpl = (rank + 31) / 32;
 #define TIB_LAT_DISPATCH(T)                                                                             \
   (dpl <= 1 ? launch_latent_attention<T, 1>(folded, pool, out, a, n_entries, max_q_len, stream)        \

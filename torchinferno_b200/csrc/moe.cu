@@ -9,10 +9,11 @@
 //                place[pair] = sorted index.  The order inside an expert may differ from run to run; every row
 //                of a product is computed by itself, so no value depends on it
 //   moe_expert_product   y[s] = act(x[src(s)] . W_e^T) for the sorted rows s of expert e; W: [experts, n, k];
-//                fp32 FMAs in fixed k order (operands float or bf16 in memory); act: none, relu^2, silu
+//                act: none, relu^2, silu.  bf16 operands whose rows are 16-byte aligned run on the tensor cores
+//                (mma.sync m16n8k16, fp32 accumulation, cp.async double buffering); everything else, and the
+//                32-bit path, on fp32 FMAs in fixed k order
 //   moe_combine  out[t] = sum_k weight[t, k] * y[place[t * top + k]]  (+ sigmoid(gate[t]) * shared[t])
-#include "common.cuh"
-#include <math_constants.h>
+#include "mma.cuh"
 
 namespace tib {
 
@@ -172,6 +173,105 @@ moe_expert_product_kernel(const TX* __restrict__ x, int64_t ldx, const TW* __res
   }
 }
 
+// The same product on tensor cores.  64 x 64 output tile, 4 warps of 32 x 32, k in steps of 32 through two
+// shared-memory stages filled by cp.async (rows of x are gathered by their source row as they are fetched).
+constexpr int TK = 32, TKP = TK + 8;      // (8 elements of padding: ldmatrix rows fall in different banks)
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+moe_expert_product_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
+                              TO* __restrict__ y, int64_t ldy, const int* __restrict__ offsets, const int* __restrict__ order,
+                              int experts, int top, int x_by_pair, int N, int K, int act) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ __align__(16) __nv_bfloat16 xs[2][GM][TKP];
+  __shared__ __align__(16) __nv_bfloat16 ws[2][GN][TKP];
+  __shared__ int src_row[GM];
+  __shared__ int tile_info[3];
+  if (threadIdx.x == 0) {
+    int tile = blockIdx.y, e = 0, found = -1, first = 0, rows = 0;
+    for (; e < experts; ++e) {
+      const int lo = offsets[e], n = offsets[e + 1] - lo;
+      const int tiles = (n + GM - 1) / GM;
+      if (tile < tiles) { found = e; first = lo + tile * GM; rows = min(GM, n - tile * GM); break; }
+      tile -= tiles;
+    }
+    tile_info[0] = found; tile_info[1] = first; tile_info[2] = rows;
+  }
+  __syncthreads();
+  const int expert = tile_info[0], first = tile_info[1], rows = tile_info[2];
+  if (expert < 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < GM) src_row[tid] = tid < rows ? (x_by_pair ? order[first + tid] / top : first + tid) : -1;
+  __syncthreads();
+  const __nv_bfloat16* we = w + (size_t)expert * N * K;
+  const int n0 = blockIdx.x * GN;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+
+  // a stage: 64 rows x 32 k of each operand = 256 pieces of 16 bytes each; 128 threads, two pieces of each a thread
+  auto fetch = [&](int stage, int k0) {
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int piece = tid + it * 128;
+      const int r = piece >> 2, c = (piece & 3) * 8;
+      const int sr = src_row[r];
+      const bool xv = sr >= 0 && k0 + c < K;
+      cp_async16(&xs[stage][r][c], x + (size_t)(xv ? sr : 0) * ldx + (xv ? k0 + c : 0), xv);
+      const bool wv = n0 + r < N && k0 + c < K;
+      cp_async16(&ws[stage][r][c], we + (size_t)(wv ? n0 + r : 0) * K + (wv ? k0 + c : 0), wv);
+    }
+    cp_async_commit();
+  };
+  const int steps = (K + TK - 1) / TK;
+  fetch(0, 0);
+  for (int ks = 0; ks < steps; ++ks) {
+    const int stage = ks & 1;
+    if (ks + 1 < steps) {
+      fetch(stage ^ 1, (ks + 1) * TK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      uint32_t a[2][4], b[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) ldmatrix_x4(a[i], &xs[stage][wm + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)      // two n-tiles of 8 per ldmatrix: (n 0-7, k lo), (n 0-7, k hi), (n 8-15, k lo), (n 8-15, k hi)
+        ldmatrix_x4(b[j], &ws[stage][wn + j * 16 + ((lane >> 4) << 3) + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+    }
+    __syncthreads();      // the stage is free for the fetch after next
+  }
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = wm + i * 16 + g + (c >> 1) * 8;
+        const int gn = n0 + wn + j * 8 + 2 * t + (c & 1);
+        if (r >= rows || gn >= N) continue;
+        float v = acc[i][j][c];
+        if (act == MOE_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+        else if (act == MOE_ACT_SILU) v = v / (1.f + expf(-v));
+        y[(size_t)(first + r) * ldy + gn] = from_f32<TO>(v);
+      }
+}
+
 // ----------------------------------------------------------------- combine
 template <typename TS, typename TO>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
@@ -222,6 +322,17 @@ TIB_API int tib_moe_expert_product(const void* x, int x_dtype, int64_t ldx, cons
   const int row_tiles = ceil_div(pairs, GM) + experts;      // at most this many tiles hold a row
   if (row_tiles > 65535) return TIB_E_SIZE;
   dim3 grid(ceil_div(N, GN), row_tiles);
+  if (x_dtype == TIB_BF16 && w_dtype == TIB_BF16 && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+    if (y_dtype == TIB_BF16)
+      TIB_LAUNCH_DEPENDENT(moe_expert_product_mma_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)x, ldx,
+                           (const __nv_bfloat16*)w, (__nv_bfloat16*)y, ldy, offsets, order, experts, top, x_by_pair, N, K, act);
+    else if (y_dtype == TIB_F32)
+      TIB_LAUNCH_DEPENDENT(moe_expert_product_mma_kernel<float>, grid, 128, 0, stream, (const __nv_bfloat16*)x, ldx,
+                           (const __nv_bfloat16*)w, (float*)y, ldy, offsets, order, experts, top, x_by_pair, N, K, act);
+    else
+      return TIB_E_DTYPE;
+    return TIB_OK;
+  }
 #define TIB_MOE_GO(TX, TW, TO)                                                                                             \
   TIB_LAUNCH_DEPENDENT((moe_expert_product_kernel<TX, TW, TO>), grid, 256, 0, stream, (const TX*)x, ldx, (const TW*)w, (TO*)y, \
                        ldy, offsets, order, experts, top, x_by_pair, N, K, act)

@@ -122,7 +122,7 @@ def lib() -> ctypes.CDLL:
                    "tib_plan_attention", "tib_plan_product", "tib_blas_gemm_batched",
                    "tib_add_pair", "tib_unit_norm_add", "tib_sigmoid_gate", "tib_gelu_gate_table", "tib_relu_squared",
                    "tib_scale_f32", "tib_pair_rows", "tib_add_vector", "tib_linear_attention", "tib_linear_attention_chunk",
-                   "tib_latent_append", "tib_latent_attention", "tib_moe_route", "tib_moe_group",
+                   "tib_latent_append", "tib_latent_attention", "tib_latent_attention_splits", "tib_moe_route", "tib_moe_group",
                    "tib_moe_expert_product", "tib_moe_combine"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
@@ -892,9 +892,12 @@ def latent_append(dkv: torch.Tensor, q: torch.Tensor, folded: torch.Tensor, keys
 
 def latent_attention(folded: torch.Tensor, keys: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor, kv_start: torch.Tensor,
                      slots: torch.Tensor, block_table: torch.Tensor, n_entries: int, max_q_len: int, heads: int, rank: int,
-                     rot: int, scale: float, error_word: torch.Tensor | None = None) -> torch.Tensor:
+                     rot: int, scale: float, error_word: torch.Tensor | None = None, max_kv_len: int = 0,
+                     force_simt: bool = False) -> torch.Tensor:
     """Causal attention of folded queries [tokens, heads, rank + rot] (fp32) over paged latent rows; the value of a
-    key is its first ``rank`` elements.  ``out``: [tokens, heads, rank] fp32."""
+    key is its first ``rank`` elements.  ``out``: [tokens, heads, rank] fp32.  A step of single tokens only
+    (``max_q_len`` 1) that names the longest context (``max_kv_len``) cuts every context into runs that go to blocks of
+    their own and are merged by a second kernel."""
     _need(folded, "folded", torch.float32), _need(out, "out", torch.float32)
     for name, t in (("q_start", q_start), ("kv_start", kv_start), ("slots", slots), ("block_table", block_table)):
         _need(t, name, torch.int32)
@@ -905,11 +908,18 @@ def latent_attention(folded: torch.Tensor, keys: torch.Tensor, out: torch.Tensor
         raise KernelError(f"latent_attention: pages of shape {tuple(keys.shape)} do not fit")
     if q_start.numel() < n_entries + 1 or kv_start.numel() < n_entries or slots.numel() < n_entries:
         raise KernelError("latent_attention: entry arrays are shorter than n_entries")
+    splits, partial = 1, None
+    if max_q_len == 1 and max_kv_len > 0 and n == n_entries:
+        splits = int(lib().tib_latent_attention_splits(c_int(n_entries), c_int(heads), c_int(max_kv_len)))
+        if splits > 1:
+            partial = torch.empty((n, heads, splits, 2 + rank), dtype=torch.float32, device=folded.device)
     _check("latent_attention", lib().tib_latent_attention(
         _ptr(folded), _ptr(keys), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(rank), c_int(rot),
-        c_int(keys.shape[2]), c_int64(keys.stride(0)), c_int(keys.shape[0]), c_float(scale), _ptr(error_word),
-        c_int(_code(keys.dtype)), _stream()))
+        c_int(keys.shape[2]), c_int64(keys.stride(0)), c_int(keys.shape[0]), c_float(scale), _ptr(partial), c_int(splits),
+        c_int(max_kv_len), c_int(int(force_simt)), _ptr(error_word), c_int(_code(keys.dtype)), _stream()))
+    if partial is not None:
+        count_launches(1)
     return out
 
 

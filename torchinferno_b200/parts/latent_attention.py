@@ -45,13 +45,15 @@ class LatentAttention(Mixer):
 
     def weight_specs(self) -> list[WeightSpec]:
         n, h, w = self.names, self.heads, self.hidden_size
-        specs = [WeightSpec(n["q"], (h * (self.dim + self.rot_dim), w)),
-                 WeightSpec(n["dkv"], (self.kv_rank + self.rot_dim, w)),
+        std, rank_std = w ** -0.5, self.kv_rank ** -0.5      # (random weights: rows of about unit size)
+        specs = [WeightSpec(n["q"], (h * (self.dim + self.rot_dim), w), std=std),
+                 WeightSpec(n["dkv"], (self.kv_rank + self.rot_dim, w), std=std),
                  WeightSpec(n["norm"], (self.kv_rank,), init="ones", role="vector"),
-                 WeightSpec(n["uk"], (h * self.dim, self.kv_rank)), WeightSpec(n["uv"], (h * self.value_dim, self.kv_rank))]
+                 WeightSpec(n["uk"], (h * self.dim, self.kv_rank), std=rank_std),
+                 WeightSpec(n["uv"], (h * self.value_dim, self.kv_rank), std=rank_std)]
         if self.gate:
-            specs.append(WeightSpec(n["g"], (h * self.value_dim, w)))
-        specs.append(WeightSpec(n["o"], (w, h * self.value_dim)))
+            specs.append(WeightSpec(n["g"], (h * self.value_dim, w), std=std))
+        specs.append(WeightSpec(n["o"], (w, h * self.value_dim), std=(h * self.value_dim) ** -0.5))
         return specs
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
@@ -89,7 +91,7 @@ class LatentAttention(Mixer):
             ops.library_gemm_batched(q_plain, self.uk_weight, folded[:, :, :c], w_kn=True)
         latent_out = torch.empty((n, h, c), dtype=torch.float32, device=x.device)
         ops.latent_attention(folded, kv.keys, latent_out, batch.q_start, batch.kv_start, batch.slots, kv.block_table,
-                             batch.n_entries, batch.max_q_len, h, c, r, self.scale, ctx.error_word)
+                             batch.n_entries, batch.max_q_len, h, c, r, self.scale, ctx.error_word, max_kv_len=batch.max_kv_len)
         heads_out = torch.empty((n, h, self.value_dim), dtype=x.dtype, device=x.device)
         if x.dtype == torch.float32:
             for j in range(h):

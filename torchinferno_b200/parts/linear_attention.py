@@ -42,11 +42,12 @@ class DecayLinearAttention(Mixer):
 
     def weight_specs(self) -> list[WeightSpec]:
         n, qk, vv = self.names, self.heads * self.key_dim, self.heads * self.value_dim
-        specs = [WeightSpec(n["q"], (qk, self.hidden_size)), WeightSpec(n["k"], (qk, self.hidden_size)),
-                 WeightSpec(n["v"], (vv, self.hidden_size))]
+        std = self.hidden_size ** -0.5          # (random weights: rows of about unit size from normed input)
+        specs = [WeightSpec(n["q"], (qk, self.hidden_size), std=std), WeightSpec(n["k"], (qk, self.hidden_size), std=std),
+                 WeightSpec(n["v"], (vv, self.hidden_size), std=std)]
         if self.gate:
-            specs.append(WeightSpec(n["g"], (vv, self.hidden_size)))
-        specs.append(WeightSpec(n["o"], (self.hidden_size, vv)))
+            specs.append(WeightSpec(n["g"], (vv, self.hidden_size), std=std))
+        specs.append(WeightSpec(n["o"], (self.hidden_size, vv), std=vv ** -0.5))
         if self.output_norm:
             specs.append(WeightSpec(n["norm"], (vv,), init="ones", role="vector"))
         return specs

@@ -42,15 +42,16 @@ class RoutedExperts(FeedForward):
 
     def weight_specs(self) -> list[WeightSpec]:
         router, _, up, down, shared, gate = self.names
-        specs = [WeightSpec(router, (self.experts, self.hidden_size))]
+        std = self.hidden_size ** -0.5          # (random weights: rows of about unit size from normed input)
+        specs = [WeightSpec(router, (self.experts, self.hidden_size), std=2 * std)]
         for e in range(self.experts):
-            specs += [WeightSpec(self._expert(e, "up"), (self.expert_size, self.hidden_size)),
-                      WeightSpec(self._expert(e, "down"), (self.hidden_size, self.expert_size))]
+            specs += [WeightSpec(self._expert(e, "up"), (self.expert_size, self.hidden_size), std=std),
+                      WeightSpec(self._expert(e, "down"), (self.hidden_size, self.expert_size), std=self.expert_size ** -0.5)]
         if self.shared_size:
-            specs += [WeightSpec(shared + up, (self.shared_size, self.hidden_size)),
-                      WeightSpec(shared + down, (self.hidden_size, self.shared_size))]
+            specs += [WeightSpec(shared + up, (self.shared_size, self.hidden_size), std=std),
+                      WeightSpec(shared + down, (self.hidden_size, self.shared_size), std=self.shared_size ** -0.5)]
             if self.shared_gate:
-                specs.append(WeightSpec(shared + gate, (1, self.hidden_size)))
+                specs.append(WeightSpec(shared + gate, (1, self.hidden_size), std=std))
         return specs
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:

@@ -41,11 +41,11 @@ class TokenSideInput(StreamStage):
 
     def weight_specs(self) -> list[WeightSpec]:
         _, gate, proj, norm = self.names
-        return [WeightSpec(gate, (self.dim, self.width)), WeightSpec(proj, (self.width, self.dim)),
+        return [WeightSpec(gate, (self.dim, self.width), std=0.2), WeightSpec(proj, (self.width, self.dim), std=0.2),
                 WeightSpec(norm, (self.width,), init="ones", role="vector")]
 
     def shared_weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec(self.names[0], (self.vocab_size, self.table_width))]
+        return [WeightSpec(self.names[0], (self.vocab_size, self.table_width), std=1.0)]
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         table, gate, proj, norm = self.names
@@ -72,8 +72,8 @@ class LoopInput(StreamStage):
         self.width, self.passes, self.names = width, passes, (in_name, step_name)
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec(self.names[0], (self.width, 2 * self.width)),
-                WeightSpec(self.names[1], (self.passes, self.width), role="vector")]
+        return [WeightSpec(self.names[0], (self.width, 2 * self.width), std=(2 * self.width) ** -0.5),
+                WeightSpec(self.names[1], (self.passes, self.width), std=0.5, role="vector")]
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         self.in_weight = LinearWeight(weights[self.names[0]], few_rows_tcgen05=None)
