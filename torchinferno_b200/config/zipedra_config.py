@@ -15,8 +15,10 @@ from torchinferno_b200.config.model_config import ConfigError
 
 MIXERS = ("lightning", "latent_attention")
 FEED_FORWARDS = ("dense", "moe")
-# positions are exact in the 32-bit floats the rotary angles are made from up to here; the design names no limit
-MAX_POSITIONS = 1 << 24
+# The design names no limit.  Positions are exact in the 32-bit floats the rotary angles are made from up to 2^24; the
+# limit given here is what block tables and default pools are sized by when the user names none
+# (EngineConfig.max_model_len).
+MAX_POSITIONS = 1 << 20
 
 
 def _need(data: Mapping[str, Any], key: str, where: str) -> Any:

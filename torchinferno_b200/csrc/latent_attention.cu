@@ -238,23 +238,31 @@ latent_attention_kernel(const float* __restrict__ folded, const T* __restrict__ 
 __global__ void latent_merge_kernel(const float* __restrict__ partial, float* __restrict__ out, int heads, int n_splits, int rank) {
   pdl_wait();
   pdl_trigger();
+  __shared__ float weight[64], sums[64];      // (at most 64 runs)
+  __shared__ float inv_total;
   const size_t row = (size_t)blockIdx.y * heads + blockIdx.x;
   const float* p = partial + row * n_splits * (2 + rank);
-  float mx = -CUDART_INF_F;
-  for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, p[(size_t)s * (2 + rank)]);
-  float total = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = p[(size_t)s * (2 + rank)];
-    if (ms != -CUDART_INF_F) total = fmaf(expf(ms - mx), p[(size_t)s * (2 + rank) + 1], total);
+  if ((int)threadIdx.x < n_splits) {
+    weight[threadIdx.x] = p[(size_t)threadIdx.x * (2 + rank)];          // (the maximum for now)
+    sums[threadIdx.x] = p[(size_t)threadIdx.x * (2 + rank) + 1];
   }
-  const float inv = 1.f / total;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float mx = -CUDART_INF_F;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, weight[s]);
+    float total = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      weight[s] = weight[s] == -CUDART_INF_F ? 0.f : expf(weight[s] - mx);
+      total = fmaf(weight[s], sums[s], total);
+    }
+    inv_total = 1.f / total;
+  }
+  __syncthreads();
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = p[(size_t)s * (2 + rank)];
-      if (ms != -CUDART_INF_F) acc = fmaf(expf(ms - mx), p[(size_t)s * (2 + rank) + 2 + c], acc);
-    }
-    out[row * rank + c] = acc * inv;
+    for (int s = 0; s < n_splits; ++s)
+      if (weight[s] != 0.f) acc = fmaf(weight[s], p[(size_t)s * (2 + rank) + 2 + c], acc);
+    out[row * rank + c] = acc * inv_total;
   }
 }
 
@@ -298,9 +306,9 @@ latent_attention_mma_kernel(const float* __restrict__ folded, const __nv_bfloat1
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
 
-  for (int e = tid; e < RB * w; e += blockDim.x) {
-    const int r = e / w, dd = e - r * w;
-    q_s[r * wp + dd] = __float2bfloat16_rn(r < nrows ? folded[((size_t)row0 * a.heads + r0 + r) * w + dd] : 0.f);
+  for (int r = warp; r < RB; r += kMmaWarps) {
+    const float* src = folded + ((size_t)row0 * a.heads + r0 + r) * w;
+    for (int dd = lane; dd < w; dd += 32) q_s[r * wp + dd] = __float2bfloat16_rn(r < nrows ? src[dd] : 0.f);
   }
   int tile_lo = 0, tile_hi = last_pos / kMmaKeys;
   if (a.partial) {      // (blocks_per_split counts runs of 32 keys; a tile is two of them)
@@ -309,23 +317,24 @@ latent_attention_mma_kernel(const float* __restrict__ folded, const __nv_bfloat1
     tile_hi = min(tile_hi, tile_lo + tiles_per_split - 1);
   }
   const int pieces_per_key = w / 8;
-  auto fetch = [&](int stage, int tile) {
+  auto fetch = [&](int stage, int tile) {      // a warp takes every fourth key, its lanes the 16-byte pieces of the row
     __nv_bfloat16* dst = k_s + (size_t)stage * kMmaKeys * wp;
-    for (int e = tid; e < kMmaKeys * pieces_per_key; e += blockDim.x) {
-      const int j = e / pieces_per_key, c = (e - j * pieces_per_key) * 8;
+    // the tile's 64 page ids first, two a lane and all in flight together: looked up key by key, every one of a
+    // warp's sixteen keys waited a memory latency of its own
+    int page_of[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int kp = tile * kMmaKeys + i * 32 + lane;
+      page_of[i] = kp <= last_pos ? table[kp / a.page_size] : -1;
+    }
+    for (int j = warp; j < kMmaKeys; j += kMmaWarps) {
       const int kp = tile * kMmaKeys + j;
-      bool valid = kp <= last_pos;
-      const __nv_bfloat16* src = pool;
-      if (valid) {
-        const int page = table[kp / a.page_size];
-        if (page >= 0 && page < a.num_pages) {
-          src = pool + (size_t)page * a.page_stride + (size_t)(kp % a.page_size) * w + c;
-        } else {
-          valid = false;
-          if (a.error_word) atomicExch(a.error_word, 0x30000 + entry);
-        }
-      }
-      cp_async16(dst + j * wp + c, src, valid);      // (not valid: zeros; such keys are always masked)
+      const int page = __shfl_sync(0xffffffffu, j < 32 ? page_of[0] : page_of[1], j & 31);
+      const bool valid = page >= 0 && page < a.num_pages;
+      if (kp <= last_pos && !valid && a.error_word && lane == 0) atomicExch(a.error_word, 0x30000 + entry);
+      const __nv_bfloat16* src = valid ? pool + (size_t)page * a.page_stride + (size_t)(kp % a.page_size) * w : pool;
+      for (int c = lane; c < pieces_per_key; c += 32)
+        cp_async16(dst + j * wp + c * 8, valid ? src + c * 8 : pool, valid);      // (not valid: zeros; such keys are always masked)
     }
     cp_async_commit();
   };
@@ -361,24 +370,37 @@ latent_attention_mma_kernel(const float* __restrict__ folded, const __nv_bfloat1
     __syncthreads();                                   // the tile (and, the first time, q_s) is in shared memory
     const __nv_bfloat16* kt = k_s + (size_t)stage * kMmaKeys * wp;
     // scores of this warp's 16 keys
-    float s[MT][2][4];
+    float s[MT][2][4], s2[MT][2][4];      // (two sets of accumulators, for even and odd steps of k: shorter chains of dependent products)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int n = 0; n < 2; ++n)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) s[mt][n][c] = 0.f;
-    for (int kk = 0; kk < w; kk += 16) {
-      uint32_t b[4];
+        for (int c = 0; c < 4; ++c) s[mt][n][c] = s2[mt][n][c] = 0.f;
+    for (int kk = 0; kk < w; kk += 32) {
+      uint32_t b[4], b2[4];
+      const bool second = kk + 16 < w;
       ldmatrix_x4(b, kt + (warp * 16 + ((lane >> 4) << 3) + (lane & 7)) * wp + kk + ((lane >> 3) & 1) * 8);
+      if (second) ldmatrix_x4(b2, kt + (warp * 16 + ((lane >> 4) << 3) + (lane & 7)) * wp + kk + 16 + ((lane >> 3) & 1) * 8);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        uint32_t qa[4];
+        uint32_t qa[4], qa2[4];
         ldmatrix_x4(qa, q_s + (mt * 16 + (lane & 15)) * wp + kk + (lane >> 4) * 8);
+        if (second) ldmatrix_x4(qa2, q_s + (mt * 16 + (lane & 15)) * wp + kk + 16 + (lane >> 4) * 8);
         mma_bf16(s[mt][0], qa, b[0], b[1]);
         mma_bf16(s[mt][1], qa, b[2], b[3]);
+        if (second) {
+          mma_bf16(s2[mt][0], qa2, b2[0], b2[1]);
+          mma_bf16(s2[mt][1], qa2, b2[2], b2[3]);
+        }
       }
     }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[mt][n][c] += s2[mt][n][c];
     const int key0 = tile * kMmaKeys + warp * 16;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -453,10 +475,13 @@ latent_attention_mma_kernel(const float* __restrict__ folded, const __nv_bfloat1
         uint32_t v[4];     // (k lo, n 0-7), (k hi, n 0-7), (k lo, n 8-15), (k hi, n 8-15), transposed on the way in
         ldmatrix_x4_trans(v, kt + (ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * wp + col0 + cg * 16 + ((lane >> 4) << 3));
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
+        for (int mt = 0; mt < MT; ++mt) {      // (the low terms after all the high ones: no product waits for the one before it)
           mma_bf16(o[mt][2 * cg], ph[mt], v[0], v[1]);
-          mma_bf16(o[mt][2 * cg], pl[mt], v[0], v[1]);
           mma_bf16(o[mt][2 * cg + 1], ph[mt], v[2], v[3]);
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(o[mt][2 * cg], pl[mt], v[0], v[1]);
           mma_bf16(o[mt][2 * cg + 1], pl[mt], v[2], v[3]);
         }
       }
@@ -563,7 +588,7 @@ TIB_API int tib_latent_attention_splits(int n_entries, int heads, int max_kv_len
   const int head_chunk = heads < kLatRows ? heads : kLatRows;
   const int blocks = n_entries * ceil_div(heads, head_chunk);
   const int key_blocks = ceil_div(max_kv_len, kLatKeys);
-  int splits = (2 * 148) / (blocks < 1 ? 1 : blocks);
+  int splits = 148 / (blocks < 1 ? 1 : blocks);      // (one block per SM: the tensor-core kernel's stages fill its shared memory)
   if (splits > key_blocks) splits = key_blocks;
   if (splits > 64) splits = 64;
   return splits < 1 ? 1 : splits;

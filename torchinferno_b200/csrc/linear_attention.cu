@@ -4,8 +4,10 @@
 // for the tokens of a ragged batch: portions of prompts and single decoded tokens alike.  An optional
 // activation (silu) is applied to q, k and v as they are read, in fp32.
 //
-// One block owns one (request entry, head).  It keeps S in shared memory and walks the entry's tokens in
-// chunks of up to C: within a chunk of n tokens
+// One block owns one (request entry, head, run of value columns): the columns of S do not depend on one another, so
+// a head is cut into runs of columns that go to blocks of their own until the grid fills the GPU (each recomputes the
+// chunk's scores, which are cheap beside the state).  A block keeps its columns of S in shared memory and walks the
+// entry's tokens in chunks of up to C: within a chunk of n tokens
 //     A[i][j] = (q_i . k_j) lambda^(i-j)                                    j <= i
 //     o_i     = lambda^(i+1) S^T q_i + sum_(j<=i) A[i][j] v_j
 //     S      <- lambda^n S + sum_j lambda^(n-1-j) k_j v_j^T
@@ -24,6 +26,7 @@ struct LinAttnArgs {
   float* out;             // [tokens, heads * value_dim]
   int64_t ldq, ldk, ldv;  // row strides of q, k, v (elements)
   int heads, key_dim, value_dim, chunk, activation;
+  int cols;               // value columns per block
 };
 
 __device__ __forceinline__ float lin_act(float z, int activation) { return activation ? z / (1.f + expf(-z)) : z; }
@@ -32,20 +35,22 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, LinAttnArgs a) {
   extern __shared__ float smem[];
-  const int D = a.key_dim, V = a.value_dim, C = a.chunk, DP = D + 1;
+  const int D = a.key_dim, C = a.chunk, DP = D + 1;
+  const int col0 = blockIdx.z * a.cols;
+  const int V = min(a.cols, a.value_dim - col0);       // this block's columns: col0 .. col0 + V - 1 of the head's value_dim
   float* S = smem;                 // [D][V]
-  float* qs = S + D * V;           // [C][DP]
+  float* qs = S + D * a.cols;      // [C][DP]
   float* ks = qs + C * DP;         // [C][DP]
   float* vs = ks + C * DP;         // [C][V]
-  float* A = vs + C * V;           // [C][C]
+  float* A = vs + C * a.cols;      // [C][C]
   float* pw = A + C * C;           // [C + 1]
   const int head = blockIdx.x, entry = blockIdx.y;
   pdl_wait();
   pdl_trigger();
   const int row0 = a.q_start[entry], len = a.q_start[entry + 1] - row0;
   if (len <= 0) return;
-  float* state = a.state + ((size_t)a.slots[entry] * a.heads + head) * D * V;
-  for (int e = threadIdx.x; e < D * V; e += blockDim.x) S[e] = state[e];
+  float* state = a.state + ((size_t)a.slots[entry] * a.heads + head) * D * a.value_dim + col0;      // row stride value_dim
+  for (int e = threadIdx.x; e < D * V; e += blockDim.x) S[e] = state[(size_t)(e / V) * a.value_dim + e % V];
   for (int e = threadIdx.x; e <= C; e += blockDim.x) pw[e] = a.powers[head * (C + 1) + e];
 
   for (int t0 = 0; t0 < len; t0 += C) {
@@ -59,7 +64,7 @@ linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     }
     for (int e = threadIdx.x; e < n * V; e += blockDim.x) {
       const int i = e / V, c = e - i * V;
-      vs[i * V + c] = lin_act(to_f32(v[(size_t)(row0 + t0 + i) * a.ldv + head * V + c]), a.activation);
+      vs[i * V + c] = lin_act(to_f32(v[(size_t)(row0 + t0 + i) * a.ldv + head * a.value_dim + col0 + c]), a.activation);
     }
     __syncthreads();
     for (int e = threadIdx.x; e < n * n; e += blockDim.x) {
@@ -77,7 +82,7 @@ linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
       float carried = 0.f, inside = 0.f;
       for (int d = 0; d < D; ++d) carried = fmaf(qs[i * DP + d], S[d * V + c], carried);
       for (int j = 0; j <= i; ++j) inside = fmaf(A[i * C + j], vs[j * V + c], inside);
-      a.out[(size_t)(row0 + t0 + i) * a.heads * V + head * V + c] = fmaf(pw[i + 1], carried, inside);
+      a.out[(size_t)(row0 + t0 + i) * a.heads * a.value_dim + head * a.value_dim + col0 + c] = fmaf(pw[i + 1], carried, inside);
     }
     __syncthreads();               // every o of the chunk has read the old S
     for (int e = threadIdx.x; e < D * V; e += blockDim.x) {
@@ -88,7 +93,7 @@ linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < D * V; e += blockDim.x) state[e] = S[e];
+  for (int e = threadIdx.x; e < D * V; e += blockDim.x) state[(size_t)(e / V) * a.value_dim + e % V] = S[e];
 }
 
 static inline size_t lin_attn_smem(int D, int V, int C) {
@@ -116,13 +121,17 @@ TIB_API int tib_linear_attention(const void* q, const void* k, const void* v, in
   if (n_entries == 0) return TIB_OK;
   if (!q || !k || !v || !out || !state || !powers || !q_start || !slots) return TIB_E_ARG;
   if (heads < 1 || key_dim < 1 || value_dim < 1 || chunk < 1 || chunk > 32 || n_entries > 65535) return TIB_E_SIZE;
-  const size_t smem = lin_attn_smem(key_dim, value_dim, chunk);
-  if (smem > 227 * 1024) return TIB_E_SMEM;
   LinAttnArgs a;
   a.q_start = q_start; a.slots = slots; a.powers = powers; a.state = state; a.out = out;
   a.ldq = ldq; a.ldk = ldk; a.ldv = ldv;
   a.heads = heads; a.key_dim = key_dim; a.value_dim = value_dim; a.chunk = chunk; a.activation = activation;
-  dim3 grid(heads, n_entries);
+  // runs of value columns: halve them (down to 8) while the grid has fewer than two blocks per SM
+  int cols = value_dim;
+  while (cols > 8 && cols % 2 == 0 && (int64_t)heads * n_entries * (value_dim / cols) < 2 * 148) cols /= 2;
+  a.cols = cols;
+  const size_t smem = lin_attn_smem(key_dim, cols, chunk);
+  if (smem > 227 * 1024) return TIB_E_SMEM;
+  dim3 grid(heads, n_entries, ceil_div(value_dim, cols));
   if (dtype == TIB_F32) {
     auto kern = linear_attention_kernel<float>;
     if (smem > 48 * 1024) {
