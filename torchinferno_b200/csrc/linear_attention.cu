@@ -41,7 +41,8 @@ linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
   float* S = smem;                 // [D][V]
   float* qs = S + D * a.cols;      // [C][DP]
   float* ks = qs + C * DP;         // [C][DP]
-  float* vs = ks + C * DP;         // [C][V]
+  float* vs = ks + C * DP;         // [C][V], on a 16-byte boundary (rows of four columns are read as one)
+  vs += (4 - (int)((vs - smem) & 3)) & 3;
   float* A = vs + C * a.cols;      // [C][C]
   float* pw = A + C * C;           // [C + 1]
   const int head = blockIdx.x, entry = blockIdx.y;
@@ -67,29 +68,81 @@ linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
       vs[i * V + c] = lin_act(to_f32(v[(size_t)(row0 + t0 + i) * a.ldv + head * a.value_dim + col0 + c]), a.activation);
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < n * n; e += blockDim.x) {
-      const int i = e / n, j = e - i * n;
-      float s = 0.f;
-      if (j <= i) {
-        for (int d = 0; d < D; ++d) s = fmaf(qs[i * DP + d], ks[j * DP + d], s);
-        s *= pw[i - j];
+    // scores: a thread takes a 2 x 2 block (rows i, i + 1; keys j, j + 1), so four products share four loads
+    {
+      const int half = (n + 1) / 2;
+      for (int e = threadIdx.x; e < half * half; e += blockDim.x) {
+        const int bi = e / half, bj = e - bi * half;
+        const int i = 2 * bi, j = 2 * bj;
+        if (j > i + 1) continue;                       // the block lies above the diagonal
+        const int i1 = min(i + 1, n - 1), j1 = min(j + 1, n - 1);
+        float s00 = 0.f, s01 = 0.f, s10 = 0.f, s11 = 0.f;
+        for (int d = 0; d < D; ++d) {
+          const float q0 = qs[i * DP + d], q1 = qs[i1 * DP + d], k0 = ks[j * DP + d], k1 = ks[j1 * DP + d];
+          s00 = fmaf(q0, k0, s00); s01 = fmaf(q0, k1, s01); s10 = fmaf(q1, k0, s10); s11 = fmaf(q1, k1, s11);
+        }
+        A[i * C + j] = j <= i ? s00 * pw[i - j] : 0.f;
+        if (j + 1 < n) A[i * C + j + 1] = j + 1 <= i ? s01 * pw[i - j - 1] : 0.f;
+        if (i + 1 < n) {
+          A[(i + 1) * C + j] = s10 * pw[i + 1 - j];
+          if (j + 1 < n) A[(i + 1) * C + j + 1] = j + 1 <= i + 1 ? s11 * pw[i - j] : 0.f;
+        }
       }
-      A[i * C + j] = s;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < n * V; e += blockDim.x) {
-      const int i = e / V, c = e - i * V;
-      float carried = 0.f, inside = 0.f;
-      for (int d = 0; d < D; ++d) carried = fmaf(qs[i * DP + d], S[d * V + c], carried);
-      for (int j = 0; j <= i; ++j) inside = fmaf(A[i * C + j], vs[j * V + c], inside);
-      a.out[(size_t)(row0 + t0 + i) * a.heads * a.value_dim + head * a.value_dim + col0 + c] = fmaf(pw[i + 1], carried, inside);
-    }
-    __syncthreads();               // every o of the chunk has read the old S
-    for (int e = threadIdx.x; e < D * V; e += blockDim.x) {
-      const int d = e / V, c = e - d * V;
-      float add = 0.f;
-      for (int j = 0; j < n; ++j) add = fmaf(pw[n - 1 - j] * ks[j * DP + d], vs[j * V + c], add);
-      S[e] = fmaf(pw[n], S[e], add);
+    if ((V & 3) == 0) {
+      // outputs and state: a thread takes four neighbouring columns (one 16-byte load of S or v per step)
+      const int V4 = V >> 2;
+      for (int e = threadIdx.x; e < n * V4; e += blockDim.x) {
+        const int i = e / V4, c = (e - i * V4) * 4;
+        float4 carried = make_float4(0.f, 0.f, 0.f, 0.f), inside = carried;
+        for (int d = 0; d < D; ++d) {
+          const float qv = qs[i * DP + d];
+          const float4 sv = *reinterpret_cast<const float4*>(S + d * V + c);
+          carried.x = fmaf(qv, sv.x, carried.x); carried.y = fmaf(qv, sv.y, carried.y);
+          carried.z = fmaf(qv, sv.z, carried.z); carried.w = fmaf(qv, sv.w, carried.w);
+        }
+        for (int j = 0; j <= i; ++j) {
+          const float av = A[i * C + j];
+          const float4 vv = *reinterpret_cast<const float4*>(vs + j * V + c);
+          inside.x = fmaf(av, vv.x, inside.x); inside.y = fmaf(av, vv.y, inside.y);
+          inside.z = fmaf(av, vv.z, inside.z); inside.w = fmaf(av, vv.w, inside.w);
+        }
+        float* dst = a.out + (size_t)(row0 + t0 + i) * a.heads * a.value_dim + head * a.value_dim + col0 + c;
+        const float pi = pw[i + 1];
+        dst[0] = fmaf(pi, carried.x, inside.x); dst[1] = fmaf(pi, carried.y, inside.y);
+        dst[2] = fmaf(pi, carried.z, inside.z); dst[3] = fmaf(pi, carried.w, inside.w);
+      }
+      __syncthreads();               // every o of the chunk has read the old S
+      for (int e = threadIdx.x; e < D * V4; e += blockDim.x) {
+        const int d = e / V4, c = (e - d * V4) * 4;
+        float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < n; ++j) {
+          const float kv = pw[n - 1 - j] * ks[j * DP + d];
+          const float4 vv = *reinterpret_cast<const float4*>(vs + j * V + c);
+          add.x = fmaf(kv, vv.x, add.x); add.y = fmaf(kv, vv.y, add.y); add.z = fmaf(kv, vv.z, add.z); add.w = fmaf(kv, vv.w, add.w);
+        }
+        float4* sp = reinterpret_cast<float4*>(S + d * V + c);
+        float4 sv = *sp;
+        const float pn = pw[n];
+        sv.x = fmaf(pn, sv.x, add.x); sv.y = fmaf(pn, sv.y, add.y); sv.z = fmaf(pn, sv.z, add.z); sv.w = fmaf(pn, sv.w, add.w);
+        *sp = sv;
+      }
+    } else {
+      for (int e = threadIdx.x; e < n * V; e += blockDim.x) {
+        const int i = e / V, c = e - i * V;
+        float carried = 0.f, inside = 0.f;
+        for (int d = 0; d < D; ++d) carried = fmaf(qs[i * DP + d], S[d * V + c], carried);
+        for (int j = 0; j <= i; ++j) inside = fmaf(A[i * C + j], vs[j * V + c], inside);
+        a.out[(size_t)(row0 + t0 + i) * a.heads * a.value_dim + head * a.value_dim + col0 + c] = fmaf(pw[i + 1], carried, inside);
+      }
+      __syncthreads();               // every o of the chunk has read the old S
+      for (int e = threadIdx.x; e < D * V; e += blockDim.x) {
+        const int d = e / V, c = e - d * V;
+        float add = 0.f;
+        for (int j = 0; j < n; ++j) add = fmaf(pw[n - 1 - j] * ks[j * DP + d], vs[j * V + c], add);
+        S[e] = fmaf(pw[n], S[e], add);
+      }
     }
   }
   __syncthreads();
@@ -97,7 +150,7 @@ linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
 }
 
 static inline size_t lin_attn_smem(int D, int V, int C) {
-  return sizeof(float) * ((size_t)D * V + 2 * (size_t)C * (D + 1) + (size_t)C * V + (size_t)C * C + C + 1);
+  return sizeof(float) * ((size_t)D * V + 2 * (size_t)C * (D + 1) + 3 + (size_t)C * V + (size_t)C * C + C + 1);
 }
 
 }  // namespace tib

@@ -17,6 +17,28 @@
 
 namespace tib {
 
+// ----------------------------------------------------------- router logits
+// out[t, e] = x[t] . w[e] in fp32 for a handful of rows w (the router, perhaps a gate row behind it): one warp per
+// (token, row), lanes stride over k, then a butterfly sum: the order of every sum is fixed by k alone, so a token's
+// logits do not depend on what else is in the step.  (The general fp32 product gives a product this narrow to a
+// single block.)
+template <typename TX>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const TX* __restrict__ x, int64_t ldx, const float* __restrict__ w, float* __restrict__ out, int64_t ldo,
+                     int rows, int K) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const TX* xr = x + (size_t)blockIdx.x * ldx;
+  for (int e = warp + blockIdx.y * nwarps; e < rows; e += nwarps * gridDim.y) {
+    const float* wr = w + (size_t)e * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(xr[k]), wr[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[(size_t)blockIdx.x * ldo + e] = acc;
+  }
+}
+
 // ------------------------------------------------------------------- route
 __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int experts, int top, int sigmoid_scores,
                                  int normalize, float norm_eps, int* __restrict__ ids, float* __restrict__ weights, int tokens) {
@@ -295,6 +317,24 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 }  // namespace tib
 
 using namespace tib;
+
+// x: [tokens, K] (row stride ldx) float or bf16; w: [rows, K] fp32; out: [tokens, rows] fp32 (row stride ldo)
+TIB_API int tib_router_logits(const void* x, int x_dtype, int64_t ldx, const float* w, float* out, int64_t ldo, int tokens,
+                              int rows, int K, cudaStream_t stream) {
+  if (tokens == 0 || rows == 0) return TIB_OK;
+  if (!x || !w || !out || tokens < 0 || rows < 0 || K < 1) return TIB_E_ARG;
+  if (tokens > 0x7fffffff / 2) return TIB_E_SIZE;
+  int slices = 1;      // few tokens: the rows of w are spread over several blocks a token
+  while (tokens * slices < 2 * 148 && slices * 8 < rows) slices *= 2;
+  dim3 grid(tokens, slices);
+  if (x_dtype == TIB_F32)
+    TIB_LAUNCH_DEPENDENT(router_logits_kernel<float>, grid, 256, 0, stream, (const float*)x, ldx, w, out, ldo, rows, K);
+  else if (x_dtype == TIB_BF16)
+    TIB_LAUNCH_DEPENDENT(router_logits_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)x, ldx, w, out, ldo, rows, K);
+  else
+    return TIB_E_DTYPE;
+  return TIB_OK;
+}
 
 TIB_API int tib_moe_route(const float* logits, int64_t ld, int tokens, int experts, int top, int sigmoid_scores, int normalize,
                           float norm_eps, int* ids, float* weights, cudaStream_t stream) {

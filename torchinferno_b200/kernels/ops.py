@@ -122,7 +122,7 @@ def lib() -> ctypes.CDLL:
                    "tib_plan_attention", "tib_plan_product", "tib_blas_gemm_batched",
                    "tib_add_pair", "tib_unit_norm_add", "tib_sigmoid_gate", "tib_gelu_gate_table", "tib_relu_squared",
                    "tib_scale_f32", "tib_pair_rows", "tib_add_vector", "tib_linear_attention", "tib_linear_attention_chunk",
-                   "tib_latent_append", "tib_latent_attention", "tib_latent_attention_splits", "tib_moe_route", "tib_moe_group",
+                   "tib_latent_append", "tib_latent_attention", "tib_latent_attention_splits", "tib_moe_route", "tib_moe_group", "tib_router_logits",
                    "tib_moe_expert_product", "tib_moe_combine"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
@@ -925,6 +925,17 @@ def latent_attention(folded: torch.Tensor, keys: torch.Tensor, out: torch.Tensor
 
 # ---------------------------------------------------------------------------
 MOE_ACT = {"none": 0, "relu2": 1, "silu": 2}
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, e] = x[t] . w[e] in fp32, for a few rows ``w`` (fp32): every sum in an order fixed by k alone."""
+    _rows_of(x, "x"), _need(w, "w", torch.float32), _rows_of(out, "out")
+    if out.dtype != torch.float32 or w.dim() != 2 or x.shape[1] != w.shape[1] or out.shape != (x.shape[0], w.shape[0]):
+        raise KernelError("router_logits: shapes or types do not fit")
+    _check("router_logits", lib().tib_router_logits(_ptr(x), c_int(_code(x.dtype)), c_int64(x.stride(0)), _ptr(w), _ptr(out),
+                                                    c_int64(out.stride(0)), c_int(x.shape[0]), c_int(w.shape[0]), c_int(x.shape[1]),
+                                                    _stream()))
+    return out
 
 
 def moe_route(logits: torch.Tensor, experts: int, top: int, ids: torch.Tensor, weights: torch.Tensor, *,

@@ -67,7 +67,7 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
         n, dev, top = x.shape[0], x.device, self.top
         logits = torch.empty((n, self.router_weight.shape[0]), dtype=torch.float32, device=dev)
-        ops.gemm_f32(x, self.router_weight, logits)
+        ops.router_logits(x, self.router_weight, logits)
         ids = torch.empty((n, top), dtype=torch.int32, device=dev)
         weights = torch.empty((n, top), dtype=torch.float32, device=dev)
         ops.moe_route(logits, self.experts, top, ids, weights, sigmoid_scores=self.scores == "sigmoid",
