@@ -54,18 +54,75 @@ linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
   for (int e = threadIdx.x; e < D * V; e += blockDim.x) S[e] = state[(size_t)(e / V) * a.value_dim + e % V];
   for (int e = threadIdx.x; e <= C; e += blockDim.x) pw[e] = a.powers[head * (C + 1) + e];
 
+  // bf16 rows on 16-byte boundaries are fetched eight elements a load, and the next chunk's rows are asked for before
+  // the current chunk is worked on (they wait in registers): fetched element by element where they were needed, the
+  // rows cost a chain of memory latencies per chunk, more than the arithmetic.
+  constexpr int kPieces = 4;       // 16-byte pieces a thread holds per tensor
+  const int dp = D / 8, vp = V / 8;
+  bool wide = false;
+  if constexpr (sizeof(T) == 2) {
+    wide = D % 8 == 0 && V % 8 == 0 && col0 % 8 == 0 && a.value_dim % 8 == 0 && a.ldq % 8 == 0 && a.ldk % 8 == 0 && a.ldv % 8 == 0 &&
+           ((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 &&
+           C * dp <= kPieces * (int)blockDim.x && C * vp <= kPieces * (int)blockDim.x;
+  }
+  uint4 rq[kPieces], rk[kPieces], rv[kPieces];
+  auto ask = [&](int t0) {
+    const int n = min(C, len - t0);
+#pragma unroll
+    for (int it = 0; it < kPieces; ++it) {
+      const int p = threadIdx.x + it * blockDim.x;
+      if (p < n * dp) {
+        const int i = p / dp, c = (p - i * dp) * 8;
+        const size_t row = row0 + t0 + i;
+        rq[it] = *reinterpret_cast<const uint4*>(q + row * a.ldq + head * D + c);
+        rk[it] = *reinterpret_cast<const uint4*>(k + row * a.ldk + head * D + c);
+      }
+      if (p < n * vp) {
+        const int i = p / vp, c = (p - i * vp) * 8;
+        rv[it] = *reinterpret_cast<const uint4*>(v + (size_t)(row0 + t0 + i) * a.ldv + head * a.value_dim + col0 + c);
+      }
+    }
+  };
+  auto unpack = [&](const uint4& raw, float* dst) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const float2 f = bf16x2_floats(h2[x]);
+      dst[2 * x] = lin_act(f.x, a.activation);
+      dst[2 * x + 1] = lin_act(f.y, a.activation);
+    }
+  };
+  if (wide) ask(0);
+
   for (int t0 = 0; t0 < len; t0 += C) {
     const int n = min(C, len - t0);
     __syncthreads();               // the chunk before is done with qs, ks, vs, A (and S, pw are loaded)
-    for (int e = threadIdx.x; e < n * D; e += blockDim.x) {
-      const int i = e / D, d = e - i * D;
-      const size_t row = row0 + t0 + i;
-      qs[i * DP + d] = lin_act(to_f32(q[row * a.ldq + head * D + d]), a.activation);
-      ks[i * DP + d] = lin_act(to_f32(k[row * a.ldk + head * D + d]), a.activation);
-    }
-    for (int e = threadIdx.x; e < n * V; e += blockDim.x) {
-      const int i = e / V, c = e - i * V;
-      vs[i * V + c] = lin_act(to_f32(v[(size_t)(row0 + t0 + i) * a.ldv + head * a.value_dim + col0 + c]), a.activation);
+    if (wide) {
+#pragma unroll
+      for (int it = 0; it < kPieces; ++it) {
+        const int p = threadIdx.x + it * blockDim.x;
+        if (p < n * dp) {
+          const int i = p / dp, c = (p - i * dp) * 8;
+          unpack(rq[it], qs + i * DP + c);
+          unpack(rk[it], ks + i * DP + c);
+        }
+        if (p < n * vp) {
+          const int i = p / vp, c = (p - i * vp) * 8;
+          unpack(rv[it], vs + i * V + c);
+        }
+      }
+      if (t0 + C < len) ask(t0 + C);
+    } else {
+      for (int e = threadIdx.x; e < n * D; e += blockDim.x) {
+        const int i = e / D, d = e - i * D;
+        const size_t row = row0 + t0 + i;
+        qs[i * DP + d] = lin_act(to_f32(q[row * a.ldq + head * D + d]), a.activation);
+        ks[i * DP + d] = lin_act(to_f32(k[row * a.ldk + head * D + d]), a.activation);
+      }
+      for (int e = threadIdx.x; e < n * V; e += blockDim.x) {
+        const int i = e / V, c = e - i * V;
+        vs[i * V + c] = lin_act(to_f32(v[(size_t)(row0 + t0 + i) * a.ldv + head * a.value_dim + col0 + c]), a.activation);
+      }
     }
     __syncthreads();
     // scores: a thread takes a 2 x 2 block (rows i, i + 1; keys j, j + 1), so four products share four loads
@@ -180,7 +237,7 @@ TIB_API int tib_linear_attention(const void* q, const void* k, const void* v, in
   a.heads = heads; a.key_dim = key_dim; a.value_dim = value_dim; a.chunk = chunk; a.activation = activation;
   // runs of value columns: halve them (down to 8) while the grid has fewer than two blocks per SM
   int cols = value_dim;
-  while (cols > 8 && cols % 2 == 0 && (int64_t)heads * n_entries * (value_dim / cols) < 2 * 148) cols /= 2;
+  while (cols >= 16 && cols % 2 == 0 && (int64_t)heads * n_entries * (value_dim / cols) < 2 * 148) cols /= 2;
   a.cols = cols;
   const size_t smem = lin_attn_smem(key_dim, cols, chunk);
   if (smem > 227 * 1024) return TIB_E_SMEM;
