@@ -430,3 +430,53 @@ def test_latent_attention_kernels_agree_with_plain_arithmetic(heads, rank, rot, 
             err = (out.cpu().double() - want).abs().max()
             # (the CUDA-core kernel keeps q in fp32: its distance from a reference with rounded q is that rounding)
             assert err <= (4e-3 if simt else 2e-4) * want.abs().max(), f"{name}, simt={simt}: {err:.3e}"
+
+
+# ------------------------------------------------------- sizes drawn at random
+def _random_config(rng):
+    """A small Zipedra configuration with sizes drawn from lists that mix multiples of 8, 16, 64 with odd ones."""
+    pick = rng.choice
+    width = pick([24, 40, 72, 96, 136])
+    layers = []
+    for _ in range(pick([2, 3])):
+        if rng.random() < 0.5:
+            heads, rot = pick([1, 2, 5]), pick([2, 4, 8, 16])
+            mixer = latent(heads, pick([4, 8, 24]), rot, pick([6, 8, 20]), pick([16, 36, 64, 128]), pick([0.1, 0.3]),
+                           base=pick([100.0, 10000.0]), rot_dims=pick([rot, rot - 2]) or 2)
+            kind = "latent_attention"
+        else:
+            heads = pick([1, 3, 4])
+            mixer = lightning(heads, pick([4, 8, 24, 40]), pick([4, 8, 12, 16, 40]), [pick([1.0, 0.999, 0.9, 0.6, 0.25]) for _ in range(heads)])
+            kind = "lightning"
+        form = pick(["dense", "moe", "moe", None])
+        experts = pick([2, 4, 7])
+        mlp = None if form is None else {"kind": "dense", "ff": pick([20, 48, 64])} if form == "dense" else \
+            moe(experts, rng.randint(1, experts), pick([8, 24, 36]), shared=pick([None, 16, 28]))
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    config = {"architecture": "Zipedra", "vocab": pick([50, 97, 128]), "width": width, "logit_scale": pick([0.5, 1.0, 3.0]),
+              "norm": {"eps": pick([1e-6, 1e-5])}, "layers": layers}
+    if rng.random() < 0.6:
+        config["token_side"] = {"dim": pick([3, 8, 12])}
+    if rng.random() < 0.6:
+        start = rng.randint(0, len(layers) - 1)
+        config["loop"] = {"start": start, "stop": rng.randint(start + 1, len(layers)), "times": pick([1, 2, 3])}
+    return config
+
+
+@pytest.mark.parametrize("draw", range(8))
+def test_sizes_drawn_at_random(draw, tmp_path):
+    """Whole prompts, portions and token-by-token decoding of models whose every size was drawn at random, in both
+    number formats (float32 row by row, bfloat16 by the statistical bound)."""
+    need_gpu()
+    import random
+    from torchinferno_b200.weights.random_init import write_random_model
+    rng = random.Random(4200 + draw)
+    config = _random_config(rng)
+    write_random_model(config, tmp_path, seed=draw)
+    requests = requests_for(config, 50 + draw, [41, 3, 70])
+    for dtype in ("float32", "bfloat16"):
+        for kind, (steps, index) in {"whole": replay_util.trace_whole(requests), "tail": replay_util.trace_tail_decode(requests, tail=12),
+                                     "portions": replay_util.trace_portions(requests, sizes=(2, 31, 3, 33, 2, 16))}.items():
+            runner = make_runner(tmp_path, dtype, replay_util.peak_tokens(steps), page_size=rng.choice([4, 16]))
+            rows = replay_util.gather(run_steps(runner, steps), index)
+            compare(rows, tmp_path, requests, dtype, f"draw {draw} {kind}")
