@@ -306,10 +306,6 @@ latent_attention_mma_kernel(const float* __restrict__ folded, const __nv_bfloat1
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
 
-  for (int r = warp; r < RB; r += kMmaWarps) {
-    const float* src = folded + ((size_t)row0 * a.heads + r0 + r) * w;
-    for (int dd = lane; dd < w; dd += 32) q_s[r * wp + dd] = __float2bfloat16_rn(r < nrows ? src[dd] : 0.f);
-  }
   int tile_lo = 0, tile_hi = last_pos / kMmaKeys;
   if (a.partial) {      // (blocks_per_split counts runs of 32 keys; a tile is two of them)
     const int tiles_per_split = (a.blocks_per_split + 1) / 2;
@@ -358,7 +354,11 @@ latent_attention_mma_kernel(const float* __restrict__ folded, const __nv_bfloat1
       qpos[mt][h] = r < nrows ? kv0 + (r0 + r) / a.heads : -1;      // -1: no key is allowed
     }
 
-  if (tile_lo <= tile_hi) fetch(0, tile_lo);
+  if (tile_lo <= tile_hi) fetch(0, tile_lo);      // (the first tile is on its way while the queries are read)
+  for (int r = warp; r < RB; r += kMmaWarps) {
+    const float* src = folded + ((size_t)row0 * a.heads + r0 + r) * w;
+    for (int dd = lane; dd < w; dd += 32) q_s[r * wp + dd] = __float2bfloat16_rn(r < nrows ? src[dd] : 0.f);
+  }
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
     const int stage = (tile - tile_lo) & 1;
     if (tile + 1 <= tile_hi) {
