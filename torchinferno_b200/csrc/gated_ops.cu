@@ -134,6 +134,18 @@ __global__ void add_vector_kernel(float* __restrict__ x, const float* __restrict
 static inline int row_threads(int width) { return width >= 1024 ? 256 : (width >= 256 ? 128 : 64); }
 static inline bool known(int dtype) { return dtype == TIB_F32 || dtype == TIB_BF16; }
 
+// out[i] = g * sigmoid(alpha * g) * (u + 1) with g = min(gu[2i], limit), u = clamp(gu[2i + 1], -limit, limit)
+__global__ void glu_clamp_kernel(const void* __restrict__ gu, int gu_dtype, void* __restrict__ out, int out_dtype, int64_t n,
+                                 float limit, float alpha) {
+  pdl_wait();
+  pdl_trigger();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float g = fminf(load_any(gu, gu_dtype, 2 * i), limit);
+    const float u = fminf(fmaxf(load_any(gu, gu_dtype, 2 * i + 1), -limit), limit);
+    store_any(out, out_dtype, i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
 }  // namespace tib
 
 using namespace tib;
@@ -185,6 +197,18 @@ TIB_API int tib_relu_squared(const void* x, int x_dtype, void* out, int out_dtyp
   if (!known(x_dtype) || !known(out_dtype)) return TIB_E_DTYPE;
   const int blocks = (int)(ceil_div64(n, 256) < 148 * 8 ? ceil_div64(n, 256) : 148 * 8);
   TIB_LAUNCH_DEPENDENT(relu_squared_kernel, blocks, 256, 0, stream, x, x_dtype, out, out_dtype, n);
+  return TIB_OK;
+}
+
+// gu: [rows, 2 * width] with (gate i, up i) side by side; out: [rows, width].
+TIB_API int tib_glu_clamp(const void* gu, int gu_dtype, void* out, int out_dtype, int rows, int width, float limit, float alpha,
+                          cudaStream_t stream) {
+  const int64_t n = (int64_t)rows * width;
+  if (n == 0) return TIB_OK;
+  if (!gu || !out || rows < 0 || width < 0) return TIB_E_ARG;
+  if (!known(gu_dtype) || !known(out_dtype)) return TIB_E_DTYPE;
+  const int blocks = (int)(ceil_div64(n, 256) < 148 * 8 ? ceil_div64(n, 256) : 148 * 8);
+  TIB_LAUNCH_DEPENDENT(glu_clamp_kernel, blocks, 256, 0, stream, gu, gu_dtype, out, out_dtype, n, limit, alpha);
   return TIB_OK;
 }
 

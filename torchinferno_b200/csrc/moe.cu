@@ -9,10 +9,13 @@
 //                place[pair] = sorted index.  The order inside an expert may differ from run to run; every row
 //                of a product is computed by itself, so no value depends on it
 //   moe_expert_product   y[s] = act(x[src(s)] . W_e^T) for the sorted rows s of expert e; W: [experts, n, k];
-//                act: none, relu^2, silu.  bf16 operands whose rows are 16-byte aligned run on the tensor cores
+//                act: none, relu^2, silu, or a clamped gated unit over (gate, up) row pairs of W (row 2i = gate i,
+//                row 2i + 1 = up i): g = min(g, limit), u = clamp(u, -limit, limit), y_i = g * sigmoid(alpha * g) * (u + 1),
+//                which leaves n / 2 columns.  `row_scale` (per pair, may be null) multiplies the fp32 sums before the
+//                activation: a router weight that belongs on the expert's input.  bf16 operands whose rows are 16-byte aligned run on the tensor cores
 //                (mma.sync m16n8k16, fp32 accumulation, cp.async double buffering); everything else, and the
 //                32-bit path, on fp32 FMAs in fixed k order
-//   moe_combine  out[t] = sum_k weight[t, k] * y[place[t * top + k]]  (+ sigmoid(gate[t]) * shared[t])
+//   moe_combine  out[t] = sum_k weight[t, k] * y[place[t * top + k]]  (+ sigmoid(gate[t]) * shared[t]); weights may be null (1)
 #include "mma.cuh"
 
 namespace tib {
@@ -115,7 +118,24 @@ moe_group_kernel(const int* __restrict__ ids, int pairs, int experts, int* __res
 
 // ---------------------------------------------------------------- products
 constexpr int GM = 64, GN = 64, GK = 16;
-enum MoeAct : int { MOE_ACT_NONE = 0, MOE_ACT_RELU2 = 1, MOE_ACT_SILU = 2 };
+enum MoeAct : int { MOE_ACT_NONE = 0, MOE_ACT_RELU2 = 1, MOE_ACT_SILU = 2, MOE_ACT_GLU_CLAMP = 3 };
+
+struct MoeEpilogue {
+  int act;
+  float limit, alpha;          // of the clamped gated unit
+  const float* row_scale;      // [pairs] or null: sorted row s is multiplied by row_scale[order[s]] before the activation
+};
+
+__device__ __forceinline__ float moe_act(float v, int act) {
+  if (act == MOE_ACT_RELU2) { v = fmaxf(v, 0.f); return v * v; }
+  if (act == MOE_ACT_SILU) return v / (1.f + expf(-v));
+  return v;
+}
+__device__ __forceinline__ float moe_glu_clamp(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
 
 // Row tile `blockIdx.y` counts tiles of GM sorted rows expert by expert; it finds its expert by walking offsets.
 // x_by_pair: source row of sorted row s is order[s] / top (the token), else s itself (rows already sorted).
@@ -123,7 +143,7 @@ template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 moe_expert_product_kernel(const TX* __restrict__ x, int64_t ldx, const TW* __restrict__ w, TO* __restrict__ y, int64_t ldy,
                           const int* __restrict__ offsets, const int* __restrict__ order, int experts, int top,
-                          int x_by_pair, int N, int K, int act) {
+                          int x_by_pair, int N, int K, MoeEpilogue ep) {
   pdl_wait();
   pdl_trigger();
   __shared__ float xs[GK][GM + 4];
@@ -183,14 +203,21 @@ moe_expert_product_kernel(const TX* __restrict__ x, int64_t ldx, const TW* __res
   for (int i = 0; i < 4; ++i) {
     const int r = ty * 4 + i;
     if (r >= rows) continue;
+    const float rs = ep.row_scale ? ep.row_scale[order[first + r]] : 1.f;
+    if (ep.act == MOE_ACT_GLU_CLAMP) {
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int gn = n0 + tx * 4 + j;
+        if (gn + 1 >= N) continue;
+        y[(size_t)(first + r) * ldy + (gn >> 1)] = from_f32<TO>(moe_glu_clamp(acc[i][j] * rs, acc[i][j + 1] * rs, ep.limit, ep.alpha));
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tx * 4 + j;
       if (gn >= N) continue;
-      float v = acc[i][j];
-      if (act == MOE_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-      else if (act == MOE_ACT_SILU) v = v / (1.f + expf(-v));
-      y[(size_t)(first + r) * ldy + gn] = from_f32<TO>(v);
+      y[(size_t)(first + r) * ldy + gn] = from_f32<TO>(moe_act(acc[i][j] * rs, ep.act));
     }
   }
 }
@@ -203,7 +230,7 @@ template <typename TO>
 __global__ void __launch_bounds__(128)
 moe_expert_product_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
                               TO* __restrict__ y, int64_t ldy, const int* __restrict__ offsets, const int* __restrict__ order,
-                              int experts, int top, int x_by_pair, int N, int K, int act) {
+                              int experts, int top, int x_by_pair, int N, int K, MoeEpilogue ep) {
   pdl_wait();
   pdl_trigger();
   __shared__ __align__(16) __nv_bfloat16 xs[2][GM][TKP];
@@ -287,10 +314,13 @@ moe_expert_product_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, 
         const int r = wm + i * 16 + g + (c >> 1) * 8;
         const int gn = n0 + wn + j * 8 + 2 * t + (c & 1);
         if (r >= rows || gn >= N) continue;
-        float v = acc[i][j][c];
-        if (act == MOE_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-        else if (act == MOE_ACT_SILU) v = v / (1.f + expf(-v));
-        y[(size_t)(first + r) * ldy + gn] = from_f32<TO>(v);
+        const float rs = ep.row_scale ? ep.row_scale[order[first + r]] : 1.f;
+        if (ep.act == MOE_ACT_GLU_CLAMP) {      // (columns 2t and 2t + 1 of a tile sit in one thread: c and c + 1)
+          if ((c & 1) == 0 && gn + 1 < N)
+            y[(size_t)(first + r) * ldy + (gn >> 1)] = from_f32<TO>(moe_glu_clamp(acc[i][j][c] * rs, acc[i][j][c + 1] * rs, ep.limit, ep.alpha));
+          continue;
+        }
+        y[(size_t)(first + r) * ldy + gn] = from_f32<TO>(moe_act(acc[i][j][c] * rs, ep.act));
       }
 }
 
@@ -307,7 +337,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     float v = 0.f;
     for (int k = 0; k < top; ++k) {
       const int s = place[t * top + k];
-      if (s >= 0) v = fmaf(weights[t * top + k], y[(size_t)s * width + c], v);
+      if (s >= 0) v = fmaf(weights ? weights[t * top + k] : 1.f, y[(size_t)s * width + c], v);
     }
     if (shared) v = fmaf(g, to_f32(shared[t * width + c]), v);
     out[t * width + c] = from_f32<TO>(v);
@@ -353,29 +383,34 @@ TIB_API int tib_moe_group(const int* ids, int pairs, int experts, int* offsets, 
   return TIB_OK;
 }
 
-// x: rows of K (row stride ldx) in x_dtype; w: [experts, N, K] in w_dtype; y: [pairs, N] (row stride ldy) in y_dtype.
+// x: rows of K (row stride ldx) in x_dtype; w: [experts, N, K] in w_dtype; y: [pairs, N] (row stride ldy) in y_dtype
+// ([pairs, N / 2] for the clamped gated unit, whose N is even); row_scale: [pairs] fp32 or null.
 TIB_API int tib_moe_expert_product(const void* x, int x_dtype, int64_t ldx, const void* w, int w_dtype, void* y, int y_dtype,
                                    int64_t ldy, const int* offsets, const int* order, int pairs, int experts, int top,
-                                   int x_by_pair, int N, int K, int act, cudaStream_t stream) {
+                                   int x_by_pair, int N, int K, int act, float limit, float alpha, const float* row_scale,
+                                   cudaStream_t stream) {
   if (pairs == 0 || N == 0) return TIB_OK;
   if (!x || !w || !y || !offsets || !order || pairs < 0 || N < 0 || K < 1 || top < 1) return TIB_E_ARG;
+  if (act < MOE_ACT_NONE || act > MOE_ACT_GLU_CLAMP || (act == MOE_ACT_GLU_CLAMP && N % 2)) return TIB_E_SIZE;
+  MoeEpilogue ep;
+  ep.act = act; ep.limit = limit; ep.alpha = alpha; ep.row_scale = row_scale;
   const int row_tiles = ceil_div(pairs, GM) + experts;      // at most this many tiles hold a row
   if (row_tiles > 65535) return TIB_E_SIZE;
   dim3 grid(ceil_div(N, GN), row_tiles);
   if (x_dtype == TIB_BF16 && w_dtype == TIB_BF16 && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0) {
     if (y_dtype == TIB_BF16)
       TIB_LAUNCH_DEPENDENT(moe_expert_product_mma_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)x, ldx,
-                           (const __nv_bfloat16*)w, (__nv_bfloat16*)y, ldy, offsets, order, experts, top, x_by_pair, N, K, act);
+                           (const __nv_bfloat16*)w, (__nv_bfloat16*)y, ldy, offsets, order, experts, top, x_by_pair, N, K, ep);
     else if (y_dtype == TIB_F32)
       TIB_LAUNCH_DEPENDENT(moe_expert_product_mma_kernel<float>, grid, 128, 0, stream, (const __nv_bfloat16*)x, ldx,
-                           (const __nv_bfloat16*)w, (float*)y, ldy, offsets, order, experts, top, x_by_pair, N, K, act);
+                           (const __nv_bfloat16*)w, (float*)y, ldy, offsets, order, experts, top, x_by_pair, N, K, ep);
     else
       return TIB_E_DTYPE;
     return TIB_OK;
   }
 #define TIB_MOE_GO(TX, TW, TO)                                                                                             \
   TIB_LAUNCH_DEPENDENT((moe_expert_product_kernel<TX, TW, TO>), grid, 256, 0, stream, (const TX*)x, ldx, (const TW*)w, (TO*)y, \
-                       ldy, offsets, order, experts, top, x_by_pair, N, K, act)
+                       ldy, offsets, order, experts, top, x_by_pair, N, K, ep)
   if (x_dtype == TIB_F32 && w_dtype == TIB_F32 && y_dtype == TIB_F32) TIB_MOE_GO(float, float, float);
   else if (x_dtype == TIB_BF16 && w_dtype == TIB_BF16 && y_dtype == TIB_BF16) TIB_MOE_GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
   else if (x_dtype == TIB_BF16 && w_dtype == TIB_BF16 && y_dtype == TIB_F32) TIB_MOE_GO(__nv_bfloat16, __nv_bfloat16, float);
@@ -390,7 +425,7 @@ TIB_API int tib_moe_combine(const float* y, const int* place, const float* weigh
                             int shared_dtype, const float* gate, int64_t ld_gate, void* out, int out_dtype, int tokens,
                             int width, cudaStream_t stream) {
   if (tokens == 0 || width == 0) return TIB_OK;
-  if (!y || !place || !weights || !out || top < 1) return TIB_E_ARG;
+  if (!y || !place || !out || top < 1) return TIB_E_ARG;
   const int threads = width >= 1024 ? 256 : 128;
 #define TIB_COMBINE_GO(TS, TO)                                                                                       \
   TIB_LAUNCH_DEPENDENT((moe_combine_kernel<TS, TO>), tokens, threads, 0, stream, y, place, weights, top, (const TS*)shared, gate, \

@@ -1,0 +1,327 @@
+// Attention whose weights are not a softmax: every visible key gets the weight sigmoid(score + bias of the head),
+// nothing is normalised over the keys, and a head's output is multiplied by a gate of its own.
+//
+//   score(i, j) = (q_i . k_j) * scale                       q, k rotated and then divided by their root mean square
+//   visible     = j <= i, and (chunk > 0) floor(i / chunk) == floor(j / chunk), and (window > 0) i - j < window
+//   o_i         = sigmoid(gate_i) * sum over visible j of sigmoid(score(i, j) + bias) * v_j
+//
+// Positions count from the start of the sequence, so a chunk's edges do not move with the way a prompt was cut.
+// Keys are `dim` wide and values `vdim`; a layer's pages hold [kv_heads][page_size][dim] keys and then
+// [kv_heads][page_size][vdim] values.  Query head h reads kv head h / (heads / kv_heads).
+//
+//   qk_norm_append     rotary encoding of part of every q and k head (pairs (i, i + rot/2) or (2i, 2i + 1), angles
+//                      fp32 position x fp32 frequency), then x / sqrt(mean(x^2) + eps) over the head (eps < 0: no
+//                      norm), all fp32; q goes to q_out, k and v (v untouched) into their page
+//   sigmoid_attention  CUDA cores, every size: one warp owns a (token, head) row and walks the keys in blocks of 32
+//                      aligned to absolute positions in rising order, so a row's sums are the same whatever the
+//                      batch holds and however the prompt was cut.  The 32-bit path.
+//   sigmoid_attention_mma   bf16 on the tensor cores (mma.sync m16n8k16): 64 query rows of one head against 64
+//                      keys a step; scores, sigmoid and mask in fp32 registers; the weights enter the second
+//                      product as two bf16 terms (high part and remainder), so that they keep 16 bits
+#include "mma.cuh"
+#include <math_constants.h>
+
+namespace tib {
+
+__device__ __forceinline__ float sig_f(float z) { return 1.f / (1.f + expf(-z)); }
+
+// ------------------------------------------------------------------ append
+struct QkAppendArgs {
+  int64_t ld;                 // elements between rows of the projection
+  int q_off, k_off, v_off;    // columns where q, k, v start in a row (k_off < 0: the row has no k and v)
+  int heads, kv_heads, dim, vdim, rot_dim, interleaved;
+  float eps;
+  const int* positions; const int* token_slot; const int* block_table; int table_stride;
+  const float* inv_freq;
+  int page_size; int64_t page_stride; int num_pages;
+  int* error_word;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_norm_append_kernel(const T* __restrict__ proj, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                      QkAppendArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ float sm[];          // cos[rot/2], sin[rot/2], then one head of floats per warp
+  const int tok = blockIdx.x;
+  const int pos = a.positions[tok];
+  const int half = a.rot_dim >> 1;
+  float* cs = sm;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cn;
+    sincosf((float)pos * a.inv_freq[i], &sn, &cn);
+    cs[i] = cn;
+    cs[half + i] = sn;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float* head = sm + 2 * half + warp * a.dim;
+  const T* row = proj + (size_t)tok * a.ld;
+  const bool write = a.k_off >= 0;
+  int page = -1, off = 0;
+  if (write) {
+    page = a.block_table[(size_t)a.token_slot[tok] * a.table_stride + pos / a.page_size];
+    off = pos % a.page_size;
+    if (page < 0 || page >= a.num_pages) {
+      if (a.error_word && threadIdx.x == 0) atomicExch(a.error_word, 1 + tok);
+      page = -1;
+    }
+  }
+  const int rot_heads = a.heads + (write ? a.kv_heads : 0);
+  for (int hh = warp; hh < rot_heads; hh += nwarps) {
+    const bool is_q = hh < a.heads;
+    const int h = is_q ? hh : hh - a.heads;
+    const T* src = row + (is_q ? a.q_off : a.k_off) + h * a.dim;
+    for (int d = lane; d < a.dim; d += 32) head[d] = to_f32(src[d]);
+    __syncwarp();
+    // rotate: lane i takes pair i
+    for (int i = lane; i < half; i += 32) {
+      const int lo_i = a.interleaved ? 2 * i : i, hi_i = a.interleaved ? 2 * i + 1 : i + half;
+      const float lo = head[lo_i], hi = head[hi_i];
+      head[lo_i] = rope_lo(lo, hi, cs[i], cs[half + i]);
+      head[hi_i] = rope_hi(lo, hi, cs[i], cs[half + i]);
+    }
+    __syncwarp();
+    float inv = 1.f;
+    if (a.eps >= 0.f) {
+      float ss = 0.f;
+      for (int d = lane; d < a.dim; d += 32) ss = fmaf(head[d], head[d], ss);
+      inv = 1.f / sqrtf(warp_sum(ss) / (float)a.dim + a.eps);
+    }
+    T* dst = nullptr;
+    if (is_q) dst = q_out + (size_t)tok * a.heads * a.dim + h * a.dim;
+    else if (page >= 0) dst = k_pages + (size_t)page * a.page_stride + ((size_t)h * a.page_size + off) * a.dim;
+    if (dst)
+      for (int d = lane; d < a.dim; d += 32) dst[d] = from_f32<T>(head[d] * inv);
+    __syncwarp();
+  }
+  if (write && page >= 0) {
+    const T* vsrc = row + a.v_off;
+    T* vdst = v_pages + (size_t)page * a.page_stride;
+    for (int w = threadIdx.x; w < a.kv_heads * a.vdim; w += blockDim.x) {
+      const int h = w / a.vdim, d = w - h * a.vdim;
+      vdst[((size_t)h * a.page_size + off) * a.vdim + d] = vsrc[w];
+    }
+  }
+}
+
+// --------------------------------------------------------------- attention
+struct SigAttnArgs {
+  const int* q_start;      // [n_entries + 1]
+  const int* kv_start;     // [n_entries] position of the entry's first query token
+  const int* slots;        // [n_entries]
+  const int* block_table; int table_stride;
+  int heads, kv_heads, dim, vdim;
+  int page_size; int64_t page_stride; int num_pages;
+  int chunk, window;       // 0: none
+  float scale;
+  const float* head_bias;  // [heads] or null
+  const void* gate; int gate_dtype; int64_t ld_gate;    // gate logits [tokens, heads] (row stride ld_gate) or null
+  int* error_word;
+};
+
+__device__ __forceinline__ int first_visible(int qpos, int chunk, int window) {
+  int lo = 0;
+  if (chunk > 0) lo = (qpos / chunk) * chunk;
+  if (window > 0) lo = max(lo, qpos - window + 1);
+  return lo;
+}
+
+constexpr int kSaWarps = 4, kSaRowsPerWarp = 4, kSaRows = kSaWarps * kSaRowsPerWarp, kSaKeys = 32;
+
+template <typename T, int VPL>
+__global__ void __launch_bounds__(kSaWarps * 32)
+sigmoid_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                              T* __restrict__ out, SigAttnArgs a, int group_chunk, int q_tile) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ float smem[];
+  const int d = a.dim, vd = a.vdim;
+  float* q_s = smem;                          // [kSaRows][d]
+  float* k_s = q_s + kSaRows * d;             // [32][d + 1]
+  float* v_s = k_s + kSaKeys * (d + 1);       // [32][vd]
+
+  const int entry = blockIdx.y;
+  const int group = a.heads / a.kv_heads;
+  const int chunks = (group + group_chunk - 1) / group_chunk;
+  const int kvh = blockIdx.z / chunks;
+  const int g0 = (blockIdx.z - kvh * chunks) * group_chunk;
+  const int gc = min(group_chunk, group - g0);
+  const int row0 = a.q_start[entry];
+  const int q_len = a.q_start[entry + 1] - row0;
+  const int t0 = blockIdx.x * q_tile;
+  if (t0 >= q_len) return;
+  const int nt = min(q_tile, q_len - t0);
+  const int nrows = nt * gc;
+  const int pos0 = a.kv_start[entry] + t0;
+  const int last_pos = pos0 + nt - 1;
+  const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q_width = a.heads * d;
+
+  for (int e = threadIdx.x; e < nrows * d; e += blockDim.x) {
+    const int r = e / d, dd = e - r * d;
+    const int t = r / gc, g = r - t * gc;
+    q_s[r * d + dd] = to_f32(q[(size_t)(row0 + t0 + t) * q_width + (kvh * group + g0 + g) * d + dd]);
+  }
+  float acc[kSaRowsPerWarp][VPL];
+#pragma unroll
+  for (int i = 0; i < kSaRowsPerWarp; ++i)
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) acc[i][j] = 0.f;
+
+  const int first_key = first_visible(pos0, a.chunk, a.window);      // (the lowest of the tile: positions rise)
+  const int b_lo = first_key / kSaKeys, b_hi = last_pos / kSaKeys;
+  for (int b = b_lo; b <= b_hi; ++b) {
+    __syncthreads();
+    for (int j = warp; j < kSaKeys; j += kSaWarps) {
+      const int kp = b * kSaKeys + j;
+      int page = -1;
+      if (kp <= last_pos && kp >= first_key) {
+        page = table[kp / a.page_size];
+        if (page < 0 || page >= a.num_pages) {
+          if (a.error_word && lane == 0) atomicExch(a.error_word, 0x10000 + entry);
+          page = -1;
+        }
+      }
+      const size_t at = (size_t)kvh * a.page_size + (kp % a.page_size);
+      const T* kr = k_pages + (size_t)max(page, 0) * a.page_stride + at * d;
+      const T* vr = v_pages + (size_t)max(page, 0) * a.page_stride + at * vd;
+      for (int dd = lane; dd < d; dd += 32) k_s[j * (d + 1) + dd] = page >= 0 ? to_f32(kr[dd]) : 0.f;
+      for (int dd = lane; dd < vd; dd += 32) v_s[j * vd + dd] = page >= 0 ? to_f32(vr[dd]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kSaRowsPerWarp; ++i) {
+      const int r = warp * kSaRowsPerWarp + i;
+      if (r >= nrows) continue;
+      const int t = r / gc, g = r - t * gc;
+      const int qpos = pos0 + t;
+      const int lo = first_visible(qpos, a.chunk, a.window);
+      if (b * kSaKeys > qpos || b * kSaKeys + kSaKeys - 1 < lo) continue;
+      const int kp = b * kSaKeys + lane;
+      const bool allowed = kp <= qpos && kp >= lo;
+      float s = 0.f;
+      const float* qr = q_s + r * d;
+      const float* kr = k_s + lane * (d + 1);
+      for (int dd = 0; dd < d; ++dd) s = fmaf(qr[dd], kr[dd], s);
+      const float bias = a.head_bias ? a.head_bias[kvh * group + g0 + g] : 0.f;
+      const float p = allowed ? sig_f(s * a.scale + bias) : 0.f;
+      for (int kk = 0; kk < kSaKeys; ++kk) {
+        const float pk = __shfl_sync(0xffffffffu, p, kk);
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+          const int dd = lane + 32 * j;
+          if (dd < vd) acc[i][j] = fmaf(pk, v_s[kk * vd + dd], acc[i][j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kSaRowsPerWarp; ++i) {
+    const int r = warp * kSaRowsPerWarp + i;
+    if (r >= nrows) continue;
+    const int t = r / gc, g = r - t * gc;
+    const int head = kvh * group + g0 + g;
+    const size_t tok = (size_t)(row0 + t0 + t);
+    float gate = 1.f;
+    if (a.gate) {
+      const float z = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[tok * a.ld_gate + head]
+                                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gate)[tok * a.ld_gate + head]);
+      gate = sig_f(z);
+    }
+    T* dst = out + tok * a.heads * vd + (size_t)head * vd;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int dd = lane + 32 * j;
+      if (dd < vd) dst[dd] = from_f32<T>(acc[i][j] * gate);
+    }
+  }
+}
+
+template <typename T, int VPL>
+static int launch_sigmoid_simt(const void* q, const void* k_pages, const void* v_pages, void* out, const SigAttnArgs& a,
+                               int n_entries, int max_q_len, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * ((size_t)kSaRows * a.dim + (size_t)kSaKeys * (a.dim + 1) + (size_t)kSaKeys * a.vdim);
+  if (smem > 227 * 1024) return TIB_E_SMEM;
+  auto kern = sigmoid_attention_simt_kernel<T, VPL>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int group = a.heads / a.kv_heads;
+  const int group_chunk = group < kSaRows ? group : kSaRows;
+  const int q_tile = kSaRows / group_chunk;
+  const int chunks = (group + group_chunk - 1) / group_chunk;
+  if ((int64_t)a.kv_heads * chunks > 65535) return TIB_E_SIZE;
+  dim3 grid(ceil_div(max_q_len, q_tile), n_entries, a.kv_heads * chunks);
+  TIB_LAUNCH_DEPENDENT(kern, grid, kSaWarps * 32, smem, stream, (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, a,
+                       group_chunk, q_tile);
+  return TIB_OK;
+}
+
+}  // namespace tib
+
+using namespace tib;
+
+// proj: [n_tokens, ld] rows holding q at q_off, k at k_off, v at v_off (k_off < 0: no k, v: nothing is stored);
+// q_out: [n_tokens, heads * dim]; k_pages / v_pages: first key / value of this layer's first page.
+TIB_API int tib_qk_norm_append(const void* proj, int64_t ld, int q_off, int k_off, int v_off, void* q_out, void* k_pages,
+                               void* v_pages, const int* positions, const int* token_slot, const int* block_table,
+                               int table_stride, const float* inv_freq, int n_tokens, int heads, int kv_heads, int dim,
+                               int vdim, int rot_dim, int interleaved, float eps, int page_size, int64_t page_stride,
+                               int num_pages, int* error_word, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return TIB_OK;
+  if (!proj || !q_out || !positions || n_tokens < 0 || heads < 1 || dim < 1) return TIB_E_ARG;
+  if (rot_dim < 0 || rot_dim % 2 || rot_dim > dim || (rot_dim > 0 && !inv_freq)) return TIB_E_SIZE;
+  if (k_off >= 0 && (!k_pages || !token_slot || !block_table || kv_heads < 1 || page_size < 1 || (vdim > 0 && !v_pages)))
+    return TIB_E_ARG;
+  QkAppendArgs a;
+  a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.heads = heads; a.kv_heads = kv_heads; a.dim = dim;
+  a.vdim = vdim; a.rot_dim = rot_dim; a.interleaved = interleaved; a.eps = eps; a.positions = positions;
+  a.token_slot = token_slot; a.block_table = block_table; a.table_stride = table_stride; a.inv_freq = inv_freq;
+  a.page_size = page_size; a.page_stride = page_stride; a.num_pages = num_pages; a.error_word = error_word;
+  const int threads = 128;
+  const size_t smem = sizeof(float) * ((size_t)rot_dim + (size_t)(threads / 32) * dim);
+  if (smem > 48 * 1024) return TIB_E_SIZE;
+  if (dtype == TIB_F32)
+    TIB_LAUNCH_DEPENDENT(qk_norm_append_kernel<float>, n_tokens, threads, smem, stream, (const float*)proj, (float*)q_out,
+                         (float*)k_pages, (float*)v_pages, a);
+  else if (dtype == TIB_BF16)
+    TIB_LAUNCH_DEPENDENT(qk_norm_append_kernel<__nv_bfloat16>, n_tokens, threads, smem, stream, (const __nv_bfloat16*)proj,
+                         (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, a);
+  else
+    return TIB_E_DTYPE;
+  return TIB_OK;
+}
+
+// q: [n_tokens, heads * dim]; out: [n_tokens, heads * vdim]; gate: [n_tokens, >= heads] logits (row stride ld_gate)
+// or null; head_bias: [heads] fp32 or null.
+TIB_API int tib_sigmoid_attention(const void* q, const void* k_pages, const void* v_pages, void* out, const int* q_start,
+                                  const int* kv_start, const int* slots, const int* block_table, int table_stride,
+                                  int n_entries, int max_q_len, int heads, int kv_heads, int dim, int vdim, int page_size,
+                                  int64_t page_stride, int num_pages, int chunk, int window, float scale,
+                                  const float* head_bias, const void* gate, int gate_dtype, int64_t ld_gate, int* error_word,
+                                  int dtype, cudaStream_t stream) {
+  if (n_entries == 0 || max_q_len == 0) return TIB_OK;
+  if (!q || !k_pages || !v_pages || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
+  if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || vdim < 1 || page_size < 1 || chunk < 0 || window < 0)
+    return TIB_E_SIZE;
+  if (vdim > 256 || dim > 512 || n_entries > 65535) return TIB_E_SIZE;
+  SigAttnArgs a;
+  a.q_start = q_start; a.kv_start = kv_start; a.slots = slots; a.block_table = block_table; a.table_stride = table_stride;
+  a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.page_size = page_size; a.page_stride = page_stride;
+  a.num_pages = num_pages; a.chunk = chunk; a.window = window; a.scale = scale; a.head_bias = head_bias; a.gate = gate;
+  a.gate_dtype = gate_dtype; a.ld_gate = ld_gate; a.error_word = error_word;
+  const int vpl = (vdim + 31) / 32;
+#define TIB_SA_DISPATCH(T)                                                                                   \
+  (vpl <= 1 ? launch_sigmoid_simt<T, 1>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream)           \
+   : vpl <= 2 ? launch_sigmoid_simt<T, 2>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream)         \
+   : vpl <= 4 ? launch_sigmoid_simt<T, 4>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream)         \
+              : launch_sigmoid_simt<T, 8>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream))
+  if (dtype == TIB_F32) return TIB_SA_DISPATCH(float);
+  if (dtype == TIB_BF16) return TIB_SA_DISPATCH(__nv_bfloat16);
+#undef TIB_SA_DISPATCH
+  return TIB_E_DTYPE;
+}

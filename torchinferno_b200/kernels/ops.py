@@ -123,7 +123,8 @@ def lib() -> ctypes.CDLL:
                    "tib_add_pair", "tib_unit_norm_add", "tib_sigmoid_gate", "tib_gelu_gate_table", "tib_relu_squared",
                    "tib_scale_f32", "tib_pair_rows", "tib_add_vector", "tib_linear_attention", "tib_linear_attention_chunk",
                    "tib_latent_append", "tib_latent_attention", "tib_latent_attention_splits", "tib_moe_route", "tib_moe_group", "tib_router_logits",
-                   "tib_moe_expert_product", "tib_moe_combine"):
+                   "tib_moe_expert_product", "tib_moe_combine", "tib_glu_clamp", "tib_layernorm", "tib_layernorm_tail",
+                   "tib_qk_norm_append", "tib_sigmoid_attention", "tib_gated_recurrence"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -924,7 +925,7 @@ def latent_attention(folded: torch.Tensor, keys: torch.Tensor, out: torch.Tensor
 
 
 # ---------------------------------------------------------------------------
-MOE_ACT = {"none": 0, "relu2": 1, "silu": 2}
+MOE_ACT = {"none": 0, "relu2": 1, "silu": 2, "glu_clamp": 3}
 
 
 def router_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -964,29 +965,40 @@ def moe_group(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: tor
 
 
 def moe_expert_product(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, top: int,
-                       *, x_by_pair: bool, act: str = "none") -> torch.Tensor:
-    """y[s] = act(x[source of s] . w[expert of s]^T) for the sorted rows s; ``w``: [experts, N, K]; ``x_by_pair``: the source
-    of sorted row s is token order[s] // top, else row s itself."""
+                       *, x_by_pair: bool, act: str = "none", limit: float = 0.0, alpha: float = 1.0,
+                       row_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """y[s] = act(row_scale[pair of s] * (x[source of s] . w[expert of s]^T)) for the sorted rows s; ``w``: [experts, N, K];
+    ``x_by_pair``: the source of sorted row s is token order[s] // top, else row s itself.  ``act="glu_clamp"``: the rows
+    of ``w`` are (gate i, up i) pairs and y has N / 2 columns: g * sigmoid(alpha g) * (u + 1) with g = min(g, limit),
+    u = clamp(u, -limit, limit).  ``row_scale``: one fp32 factor per (token, choice) pair, or None."""
     _rows_of(x, "x"), _need(w, "w"), _rows_of(y, "y")
     experts, n, k = w.shape
     pairs = order.numel()
-    if x.shape[1] != k or y.shape != (pairs, n) or offsets.numel() != experts + 1:
+    if x.shape[1] != k or y.shape != (pairs, n // 2 if act == "glu_clamp" else n) or offsets.numel() != experts + 1:
         raise KernelError("moe_expert_product: shapes do not fit")
+    if row_scale is not None:
+        _need(row_scale, "row_scale", torch.float32)
+        if row_scale.numel() != pairs:
+            raise KernelError("moe_expert_product: row_scale must hold one factor per pair")
     _check("moe_expert_product", lib().tib_moe_expert_product(
         _ptr(x), c_int(_code(x.dtype)), c_int64(x.stride(0)), _ptr(w), c_int(_code(w.dtype)), _ptr(y), c_int(_code(y.dtype)),
         c_int64(y.stride(0)), _ptr(offsets), _ptr(order), c_int(pairs), c_int(experts), c_int(top), c_int(int(x_by_pair)),
-        c_int(n), c_int(k), c_int(MOE_ACT[act]), _stream()))
+        c_int(n), c_int(k), c_int(MOE_ACT[act]), c_float(limit), c_float(alpha), _ptr(row_scale), _stream()))
     return y
 
 
-def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, shared: torch.Tensor | None = None,
-                gate: torch.Tensor | None = None) -> torch.Tensor:
+def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor,
+                shared: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = sum_k weights[t, k] * y[place[t, k]] (+ sigmoid(gate[t]) * shared[t]); ``gate``: one fp32 logit per token
-    (a column view is fine)."""
-    _need(y, "y", torch.float32), _need(place, "place", torch.int32), _need(weights, "weights", torch.float32), _need(out, "out")
+    (a column view is fine); ``weights`` None: every weight is 1 (``place`` then is [tokens, top])."""
+    _need(y, "y", torch.float32), _need(place, "place", torch.int32), _need(out, "out")
     n, width = out.shape
-    top = weights.shape[1]
-    if y.shape[1] != width or weights.shape[0] != n or place.numel() != n * top:
+    if weights is not None:
+        _need(weights, "weights", torch.float32)
+        top = weights.shape[1]
+    else:
+        top = place.numel() // max(n, 1)
+    if y.shape[1] != width or (weights is not None and weights.shape[0] != n) or place.numel() != n * top:
         raise KernelError("moe_combine: shapes do not fit")
     if shared is not None:
         _need(shared, "shared")
@@ -1000,4 +1012,155 @@ def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, out
     _check("moe_combine", lib().tib_moe_combine(
         _ptr(y), _ptr(place), _ptr(weights), c_int(top), _ptr(shared), c_int(_code(shared.dtype) if shared is not None else 0),
         _ptr(gate), c_int64(ld_gate), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _stream()))
+    return out
+
+
+def glu_clamp(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """out[t, i] = g * sigmoid(alpha g) * (u + 1) with g = min(gate_up[t, 2i], limit), u = clamp(gate_up[t, 2i + 1], -limit, limit)."""
+    _need(gate_up, "gate_up"), _need(out, "out")
+    n, width = out.shape
+    if gate_up.shape != (n, 2 * width):
+        raise KernelError("glu_clamp: gate_up must be [rows, 2 * width]")
+    _check("glu_clamp", lib().tib_glu_clamp(_ptr(gate_up), c_int(_code(gate_up.dtype)), _ptr(out), c_int(_code(out.dtype)), c_int(n),
+                                            c_int(width), c_float(limit), c_float(alpha), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Layer norm with weight and bias, the tails of sublayers and layers built on it (csrc/layernorm.cu).
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: torch.Tensor | None = None) -> torch.Tensor:
+    """out[i] = LN(x[rows[i]] or x[i]) in fp32; x: fp32 or bf16 rows (any row stride), out: [n, width] in its own type."""
+    _rows_of(x, "x"), _need(weight, "weight", torch.float32), _need(bias, "bias", torch.float32), _need(out, "out")
+    width = x.shape[1]
+    n = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if out.shape != (n, width) or weight.numel() != width or bias.numel() != width:
+        raise KernelError("layernorm: shapes do not fit")
+    _check("layernorm", lib().tib_layernorm(_ptr(x), c_int(_code(x.dtype)), c_int64(x.stride(0)), _ptr(rows), _ptr(weight), _ptr(bias),
+                                            c_float(eps), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(width), _stream()))
+    return out
+
+
+def layernorm_tail(residual: torch.Tensor, eps: float, *, y: torch.Tensor | None = None, y_norm: tuple | None = None,
+                   history: torch.Tensor | None = None, coef: torch.Tensor | None = None, count: int = 0,
+                   out: torch.Tensor | None = None, out_norm: tuple | None = None) -> None:
+    """What follows a sublayer, in one launch: ``residual += LN(y; *y_norm)`` (if ``y``); then, if ``history``
+    ([depth, n, width] fp32 whose slice ``count - 1`` is ``residual``), ``history[count] = sum_j coef[j] * history[j]``
+    over j < count; then, if ``out``, ``out = LN(the row at hand; *out_norm)``.  Norms are (weight, bias) in fp32."""
+    _need(residual, "residual", torch.float32)
+    n, width = residual.shape
+    wa = ba = wb = bb = None
+    if y is not None:
+        _rows_of(y, "y", width)
+        wa, ba = y_norm
+        if y.shape[0] != n or wa.numel() != width or ba.numel() != width or wa.dtype != torch.float32 or ba.dtype != torch.float32:
+            raise KernelError("layernorm_tail: y or its norm do not fit")
+    slice_elems = 0
+    if history is not None:
+        _need(history, "history", torch.float32), _need(coef, "coef", torch.float32)
+        if (history.dim() != 3 or history.shape[1:] != (n, width) or not 1 <= count < history.shape[0] or coef.numel() < count
+                or history[count - 1].data_ptr() != residual.data_ptr()):
+            raise KernelError("layernorm_tail: the history does not fit")
+        slice_elems = history.stride(0)
+    if out is not None:
+        _need(out, "out")
+        wb, bb = out_norm
+        if out.shape != (n, width) or wb.numel() != width or bb.numel() != width or wb.dtype != torch.float32 or bb.dtype != torch.float32:
+            raise KernelError("layernorm_tail: out or its norm do not fit")
+    _check("layernorm_tail", lib().tib_layernorm_tail(
+        _ptr(y), c_int(_code(y.dtype) if y is not None else 0), c_int64(y.stride(0) if y is not None else 0), _ptr(wa), _ptr(ba),
+        _ptr(residual), _ptr(history), c_int64(slice_elems), _ptr(coef), c_int(count), _ptr(wb), _ptr(bb), _ptr(out),
+        c_int(_code(out.dtype) if out is not None else 0), c_int(n), c_int(width), c_float(eps), _stream()))
+
+
+# ---------------------------------------------------------------------------
+# Attention with sigmoid weights (csrc/sigmoid_attention.cu).
+def qk_norm_append(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, keys: torch.Tensor | None,
+                   values: torch.Tensor | None, positions: torch.Tensor, token_slot: torch.Tensor | None,
+                   block_table: torch.Tensor | None, inv_freq: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                   *, rot_dim: int, interleaved: bool = False, eps: float = -1.0, error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate part of every q and k head of the fused projection ``proj`` (columns q_off.., k_off.., v_off..), divide each
+    head by its root mean square (``eps`` < 0: not), write q to ``q_out`` and k, v into their pages (``keys`` /
+    ``values``: [pages, kv_heads, page_size, dim / vdim] views of one layer's pages).  ``keys`` None: only q."""
+    _rows_of(proj, "proj"), _need(q_out, "q_out", proj.dtype), _need(positions, "positions", torch.int32)
+    n = proj.shape[0]
+    if q_out.shape != (n, heads * dim):
+        raise KernelError("qk_norm_append: q_out must be [tokens, heads * dim]")
+    write = keys is not None
+    page_size = page_stride = num_pages = table_stride = 0
+    if write:
+        if keys.dtype != proj.dtype or values is None or values.dtype != proj.dtype:
+            raise KernelError("qk_norm_append: the pages must have the projection's type")
+        if keys.shape[1:] != (kv_heads, keys.shape[2], dim) or values.shape[1:] != (kv_heads, keys.shape[2], vdim) \
+                or keys.stride(0) != values.stride(0) or not keys[0].is_contiguous() or not values[0].is_contiguous():
+            raise KernelError("qk_norm_append: keys / values are not one layer's pages")
+        _need(token_slot, "token_slot", torch.int32), _need(block_table, "block_table", torch.int32)
+        num_pages, page_size, page_stride, table_stride = keys.shape[0], keys.shape[2], keys.stride(0), block_table.stride(0)
+    _check("qk_norm_append", lib().tib_qk_norm_append(
+        _ptr(proj), c_int64(proj.stride(0)), c_int(q_off), c_int(k_off if write else -1), c_int(v_off), _ptr(q_out),
+        _ptr(keys), _ptr(values), _ptr(positions), _ptr(token_slot if write else None), _ptr(block_table if write else None),
+        c_int(table_stride), _ptr(inv_freq), c_int(n), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(rot_dim),
+        c_int(int(interleaved)), c_float(eps), c_int(page_size), c_int64(page_stride), c_int(num_pages), _ptr(error_word),
+        c_int(_code(proj.dtype)), _stream()))
+    return q_out
+
+
+def sigmoid_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor,
+                      kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int, max_q_len: int,
+                      heads: int, kv_heads: int, *, scale: float, chunk: int = 0, window: int = 0,
+                      head_bias: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                      error_word: torch.Tensor | None = None) -> torch.Tensor:
+    """out[i] = sigmoid(gate[i]) * sum over visible j of sigmoid(q_i . k_j * scale + head_bias) * v_j, per head; visible:
+    j <= i, in i's chunk of ``chunk`` positions (0: no chunks) and within ``window`` (0: none).  ``gate``: [tokens, heads]
+    logits (a column slice is fine) or None."""
+    _need(q, "q"), _need(out, "out", q.dtype)
+    dim, vdim, page_size = keys.shape[3], values.shape[3], keys.shape[2]
+    n = q.shape[0]
+    if q.shape != (n, heads * dim) or out.shape != (n, heads * vdim) or keys.dtype != q.dtype or values.dtype != q.dtype:
+        raise KernelError("sigmoid_attention: shapes or types do not fit")
+    if keys.stride(0) != values.stride(0) or not keys[0].is_contiguous() or not values[0].is_contiguous():
+        raise KernelError("sigmoid_attention: keys / values are not one layer's pages")
+    if head_bias is not None:
+        _need(head_bias, "head_bias", torch.float32)
+    if gate is not None:
+        _rows_of(gate, "gate", heads)
+    _check("sigmoid_attention", lib().tib_sigmoid_attention(
+        _ptr(q), _ptr(keys), _ptr(values), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
+        c_int(page_size), c_int64(keys.stride(0)), c_int(keys.shape[0]), c_int(chunk), c_int(window), c_float(scale),
+        _ptr(head_bias), _ptr(gate), c_int(_code(gate.dtype) if gate is not None else 0),
+        c_int64(gate.stride(0) if gate is not None else 0), _ptr(error_word), c_int(_code(q.dtype)), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+GATED_RECURRENCE_RUN = 64       # tokens of a portion that one thread scans; longer portions are scanned run by run, side by side
+
+
+def gated_recurrence(proj: torch.Tensor, z_off: int, u_off: int, g_off: int, bias_z: torch.Tensor | None,
+                     bias_u: torch.Tensor | None, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+                     out: torch.Tensor, n_entries: int, max_q_len: int, run_len: int = GATED_RECURRENCE_RUN) -> torch.Tensor:
+    """The element-wise gated recurrence S = (1 - z) S + z c over each entry's tokens, from and to ``state[slot]`` (fp32);
+    z = sigmoid(proj[:, z_off..] + bias_z), c from proj[:, u_off..] + bias_u, out = S * silu(proj[:, g_off..]) (g_off < 0: S)."""
+    _rows_of(proj, "proj"), _need(state, "state", torch.float32), _need(out, "out")
+    width = out.shape[1]
+    if out.shape[0] != proj.shape[0] or state.dim() != 2 or state.shape[1] != width:
+        raise KernelError("gated_recurrence: shapes do not fit")
+    for b in (bias_z, bias_u):
+        if b is not None:
+            _need(b, "bias", torch.float32)
+    runs = -(-max_q_len // run_len)
+    run_a = run_b = None
+    if runs > 1:
+        scratch = torch.empty((2, n_entries, runs, width), dtype=torch.float32, device=out.device)
+        run_a, run_b = scratch[0], scratch[1]
+    status = lib().tib_gated_recurrence(
+        _ptr(proj), c_int(_code(proj.dtype)), c_int64(proj.stride(0)), c_int(z_off), c_int(u_off), c_int(g_off), _ptr(bias_z),
+        _ptr(bias_u), _ptr(state), _ptr(q_start), _ptr(slots), _ptr(out), c_int(_code(out.dtype)), _ptr(run_a), _ptr(run_b),
+        c_int(n_entries), c_int(max_q_len), c_int(width), c_int(run_len), _stream())
+    _check("gated_recurrence", status)
+    if runs > 1:
+        count_launches(1)
     return out

@@ -140,9 +140,23 @@ class CausalLM:
     def forward(self, batch, cache) -> torch.Tensor:
         """Run the tokens of ``batch``; return fp32 logits [len(batch.logit_rows), vocab]."""
         n = batch.n_tokens
-        residual = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.device)
+        depth = self.spec.history_depth
+        history = None
+        if depth:
+            if depth < 2:
+                raise ValueError("history_depth counts the embedding output and at least one slice to work in")
+            history = torch.empty((depth, n, self.spec.hidden_size), dtype=torch.float32, device=self.device)
+            residual = history[0]
+        else:
+            residual = torch.empty((n, self.spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(batch.token_ids, self.embedding, residual)
+        if self.spec.embedding_scale != 1.0:
+            ops.scale_(residual, self.spec.embedding_scale)
+        if depth:
+            history[1].copy_(residual)
+            residual = history[1]
         stream = ResidualStream(residual, self.dtype)
+        stream.history = history
         if self.spec.keeps_embedding_output:
             stream.origin = residual.clone()
         if self.after_embedding is not None:

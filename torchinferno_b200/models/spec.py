@@ -53,6 +53,10 @@ class ModelSpec:
     stages: tuple[PartSpec, ...] = ()         # category "stream_stage"; each prefix is a full name prefix
     logit_scale: float = 1.0                  # the head's output is multiplied by this
     keeps_embedding_output: bool = False      # stages read the embedding output (``ResidualStream.origin``)
+    embedding_scale: float = 1.0              # the embedding output is multiplied by this
+    history_depth: int = 0                    # > 0: the residual stream lives in a [depth, tokens, hidden] tensor whose
+                                              # slice 0 keeps the embedding output and whose later slices keep what
+                                              # blocks leave there (``ResidualStream.history``); the stream starts in slice 1
 
     def __post_init__(self) -> None:
         for call in self.schedule:

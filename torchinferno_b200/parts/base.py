@@ -41,7 +41,7 @@ class WeightSpec:
     """One tensor a part reads from the checkpoint, by name relative to its prefix."""
     name: str
     shape: tuple[int, ...]
-    init: str = "normal"       # random mode: "normal" (std), "ones", "zeros"
+    init: str = "normal"       # random mode: "normal" (std), "about_one" (1 + normal), "ones", "zeros"
     std: float = 0.02
     role: str = "matrix"       # "matrix": kept as stored (bf16 / fp32); "vector": widened to fp32;
                                # "int_table": integer table kept as int32
@@ -114,6 +114,10 @@ class ResidualStream:
         self.pending: torch.Tensor | None = None
         self.dtype = dtype              # activation dtype of normalised rows
         self.origin: torch.Tensor | None = None    # the embedding output, kept when the model's stages read it
+        # [depth, tokens, hidden] fp32 when the model keeps every layer's output (ModelSpec.history_depth): slice 0 is
+        # the embedding output, and ``residual`` is one of its slices; a block that averages over the layers so
+        # far reads the slices below its own and moves ``residual`` on to the next
+        self.history: torch.Tensor | None = None
         # the residual rows in the activation type, left by whoever last changed the residual and had them at
         # hand; whoever changes the residual next drops it
         self.activation_copy: torch.Tensor | None = None
@@ -257,5 +261,5 @@ def _ensure_builtin() -> None:
     if _loaded:
         return
     _loaded = True
-    from torchinferno_b200.parts import (attention, block, latent_attention, linear_attention, mlp, moe, norm,  # noqa: F401
-                                         parallel_block, rope, stream_stages)
+    from torchinferno_b200.parts import (attention, block, gated_recurrence, latent_attention, linear_attention, mlp,  # noqa: F401
+                                         moe, norm, parallel_block, rope, sandwich_block, sigmoid_attention, stream_stages)

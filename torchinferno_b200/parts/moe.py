@@ -6,6 +6,12 @@ are chosen (lowest index first among equals); their weights are the scores, divi
 the output is the weighted sum of the chosen experts' outputs.  An optional shared expert of the same form
 runs for every token and is added, multiplied by sigmoid(w_sg . x) when it has a gate row.
 
+``activation="glu_clamp"`` makes an expert a clamped gated unit: g = min(W_gate x, limit), u = clamp(W_up x, -limit,
+limit), y = g * sigmoid(alpha g) * (u + 1), output W_down y (``limit`` / ``shared_limit``, ``alpha``); gate and up run
+as one product over row pairs (gate i, up i).  ``weight_on_input``: the router weight multiplies the expert's input
+instead of its output, sum of expert(w x); it is applied to the 32-bit sums of the first product, ahead of the clamps
+(W (w x) = w (W x)), so the input rows are not rounded a second time.
+
 The pairs (token, choice) are sorted by expert on the device and both products run over the sorted rows
 (csrc/moe.cu); no count comes back to the host, so a step with this part may be captured.
 """
@@ -24,30 +30,40 @@ class RoutedExperts(FeedForward):
     def __init__(self, *, hidden_size: int, experts: int, top: int, expert_size: int, activation: str = "relu2",
                  scores: str = "softmax", normalize: bool = True, norm_eps: float = 0.0, shared_size: int = 0,
                  shared_gate: bool = False, router_name: str = "router", expert_prefix: str = "e", up_name: str = "up",
-                 down_name: str = "down", shared_prefix: str = "shared.", shared_gate_name: str = "sg",
+                 down_name: str = "down", shared_prefix: str = "shared.", shared_gate_name: str = "sg", gate_name: str = "gate",
+                 limit: float = 0.0, shared_limit: float | None = None, alpha: float = 1.702, weight_on_input: bool = False,
                  dtype: torch.dtype, device: torch.device) -> None:
         super().__init__(dtype=dtype, device=device)
         if not 1 <= top <= experts:
             raise ValueError("top must be between 1 and the number of experts")
-        if activation not in ("relu2", "silu") or scores not in ("softmax", "sigmoid"):
+        if activation not in ("relu2", "silu", "glu_clamp") or scores not in ("softmax", "sigmoid"):
             raise ValueError(f"unknown activation {activation!r} or scores {scores!r}")
         self.hidden_size, self.experts, self.top, self.expert_size = hidden_size, experts, top, expert_size
         self.activation, self.scores, self.normalize, self.norm_eps = activation, scores, bool(normalize), float(norm_eps)
         self.shared_size, self.shared_gate = int(shared_size or 0), bool(shared_gate and shared_size)
         self.names = (router_name, expert_prefix, up_name, down_name, shared_prefix, shared_gate_name)
+        self.gate_name, self.glu = gate_name, activation == "glu_clamp"
+        self.limit, self.alpha, self.weight_on_input = float(limit), float(alpha), bool(weight_on_input)
+        self.shared_limit = self.limit if shared_limit is None else float(shared_limit)
+        if self.glu and not self.limit > 0:
+            raise ValueError("the clamped gated unit needs a positive limit")
 
     def _expert(self, e: int, which: str) -> str:
         _, prefix, up, down, _, _ = self.names
-        return f"{prefix}{e}.{up if which == 'up' else down}"
+        return f"{prefix}{e}.{ {'up': up, 'down': down, 'gate': self.gate_name}[which] }"
 
     def weight_specs(self) -> list[WeightSpec]:
         router, _, up, down, shared, gate = self.names
         std = self.hidden_size ** -0.5          # (random weights: rows of about unit size from normed input)
         specs = [WeightSpec(router, (self.experts, self.hidden_size), std=2 * std)]
         for e in range(self.experts):
+            if self.glu:
+                specs.append(WeightSpec(self._expert(e, "gate"), (self.expert_size, self.hidden_size), std=std))
             specs += [WeightSpec(self._expert(e, "up"), (self.expert_size, self.hidden_size), std=std),
                       WeightSpec(self._expert(e, "down"), (self.hidden_size, self.expert_size), std=self.expert_size ** -0.5)]
         if self.shared_size:
+            if self.glu:
+                specs.append(WeightSpec(shared + self.gate_name, (self.shared_size, self.hidden_size), std=std))
             specs += [WeightSpec(shared + up, (self.shared_size, self.hidden_size), std=std),
                       WeightSpec(shared + down, (self.hidden_size, self.shared_size), std=self.shared_size ** -0.5)]
             if self.shared_gate:
@@ -58,10 +74,18 @@ class RoutedExperts(FeedForward):
         router, _, up, down, shared, gate = self.names
         rows = [weights[router]] + ([weights[shared + gate]] if self.shared_gate else [])
         self.router_weight = torch.cat(rows, dim=0).to(torch.float32).contiguous()      # (the router is fp32 in both modes)
-        self.up_weight = torch.stack([weights[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
+        def first(name_of) -> torch.Tensor:
+            """The first product's matrix: up, or (gate i, up i) row pairs for the gated unit."""
+            if not self.glu:
+                return name_of("up")
+            g, u = name_of("gate"), name_of("up")
+            return torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1])
+
+        self.up_weight = torch.stack([first(lambda which, e=e: weights[self._expert(e, which)]) for e in range(self.experts)]).contiguous()
         self.down_weight = torch.stack([weights[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
         if self.shared_size:
-            self.shared_up_weight = LinearWeight(weights[shared + up], few_rows_tcgen05=None)
+            self.shared_up_weight = LinearWeight(first(lambda which: weights[shared + {"up": up, "gate": self.gate_name}[which]]),
+                                                 few_rows_tcgen05=None)
             self.shared_down_weight = LinearWeight(weights[shared + down], few_rows_tcgen05=None)
 
     def forward(self, x: torch.Tensor, ctx: LayerContext) -> torch.Tensor:
@@ -77,7 +101,8 @@ class RoutedExperts(FeedForward):
         place = torch.empty(n * top, dtype=torch.int32, device=dev)
         ops.moe_group(ids, self.experts, offsets, order, place)
         inner = torch.empty((n * top, self.expert_size), dtype=x.dtype, device=dev)
-        ops.moe_expert_product(x, self.up_weight, inner, offsets, order, top, x_by_pair=True, act=self.activation)
+        ops.moe_expert_product(x, self.up_weight, inner, offsets, order, top, x_by_pair=True, act=self.activation,
+                               limit=self.limit, alpha=self.alpha, row_scale=weights.view(-1) if self.weight_on_input else None)
         outer = torch.empty((n * top, self.hidden_size), dtype=torch.float32, device=dev)
         ops.moe_expert_product(inner, self.down_weight, outer, offsets, order, top, x_by_pair=False)
         shared_rows = None
@@ -85,12 +110,16 @@ class RoutedExperts(FeedForward):
             hidden = linear(x, self.shared_up_weight)
             if self.activation == "relu2":
                 ops.relu_squared(hidden, hidden)
+            elif self.glu:
+                hidden = ops.glu_clamp(hidden, torch.empty((n, self.shared_size), dtype=hidden.dtype, device=dev),
+                                       self.shared_limit, self.alpha)
             else:
                 raise NotImplementedError("a shared expert with silu")
             shared_rows = linear(hidden, self.shared_down_weight)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=dev)
         gate = logits[:, self.experts] if self.shared_gate else None
-        return ops.moe_combine(outer, place, weights, out, shared_rows, gate)
+        return ops.moe_combine(outer, place.view(n, top) if self.weight_on_input else place,
+                               None if self.weight_on_input else weights, out, shared_rows, gate)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -1,4 +1,4 @@
-"""RMSNorm, plain and fused with the residual add.
+"""RMSNorm, plain and fused with the residual add; layer norm with weight and bias.
 
 y = x * rsqrt(mean(x^2) + eps) * w with the statistics, the product and the
 residual sum in fp32 (src/torchinferno/models/llama3/raw_ops.py:9-11,
@@ -39,4 +39,42 @@ class RMSNorm(Norm):
         return ops.rmsnorm(x, self.weight, self.eps, torch.empty_like(x))
 
 
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(mean of squared deviations + eps) * w + b, statistics and scaling in fp32
+    (csrc/layernorm.cu).  ``bias_name`` defaults to the weight's name with ``.b`` added."""
+
+    def __init__(self, *, width: int, eps: float, weight_name: str = "weight", bias_name: str | None = None,
+                 dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        self.width, self.eps, self.weight_name = int(width), float(eps), weight_name
+        self.bias_name = weight_name + ".b" if bias_name is None else bias_name
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return [WeightSpec(self.weight_name, (self.width,), init="about_one", std=0.1, role="vector"),
+                WeightSpec(self.bias_name, (self.width,), std=0.1, role="vector")]
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        self.weight = weights[self.weight_name].to(torch.float32).contiguous()
+        self.bias = weights[self.bias_name].to(torch.float32).contiguous()
+
+    def forward(self, residual, out, rows=None):
+        return ops.layernorm(residual, self.weight, self.bias, self.eps, out, rows)
+
+    def add_forward(self, delta, residual, out, rows=None):
+        if rows is None:
+            ops.add_pair(residual, delta)
+            return ops.layernorm(residual, self.weight, self.bias, self.eps, out)
+        # (with rows the delta is only looked at and stays pending)
+        index = rows.long()
+        picked = residual.index_select(0, index) + delta.index_select(0, index).to(torch.float32)
+        return ops.layernorm(picked, self.weight, self.bias, self.eps, out)
+
+    def forward_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """Norm rows held in the activation type (not the residual stream)."""
+        return ops.layernorm(x, self.weight, self.bias, self.eps, torch.empty_like(x))
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

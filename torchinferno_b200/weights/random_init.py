@@ -1,4 +1,4 @@
-"""Random weights: every matrix N(0, std) and every norm vector 1, from a seed.
+"""Random weights: every matrix N(0, std), norm vectors 1 (or 1 + N(0, std) where a part asks for it), from a seed.
 
 Each tensor has a generator of its own, keyed by (seed, tensor name), so a
 tensor's values do not depend on which other tensors exist or on their order.
@@ -30,12 +30,14 @@ def random_tensor(spec, seed: int, *, device: torch.device | str = "cpu",
         return torch.ones(spec.shape, dtype=dtype, device=device)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=dtype, device=device)
-    if spec.init != "normal":
+    if spec.init not in ("normal", "about_one"):
         raise ValueError(f"unknown init {spec.init!r} for {spec.name}")
     generator = torch.Generator(device=device)
     generator.manual_seed(_tensor_seed(seed, spec.name))
     out = torch.empty(spec.shape, dtype=torch.float32, device=device)
     out.normal_(0.0, spec.std, generator=generator)
+    if spec.init == "about_one":
+        out += 1.0
     return out.to(dtype)
 
 
