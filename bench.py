@@ -435,11 +435,21 @@ def design_configs() -> dict:
              "intermediate_size": 8192, "num_hidden_layers": DESIGN_LAYERS, "num_attention_heads": DESIGN_HEADS,
              "num_key_value_heads": 8, "head_dim": 128, "max_position_embeddings": 8192, "rope_theta": 500000.0,
              "rope_scaling": None, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
-    return {"zipedra": zipedra, "llama": llama}
+    # Giforax beside the same Llama: the same head counts and head size in chunks of 512 positions, a second attention
+    # layer that reads the first one's keys, a recurrence as wide as the model, routed experts of the same sizes
+    sigmoid = {"heads": DESIGN_HEADS, "kv_heads": 8, "dim": 128, "vdim": 128, "mask": {"size": 512}, "scale": 0.09,
+               "rot": {"base": 500000.0, "dims": 64}}
+    gated = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": 1024, "limit": 7.0}, "shared": {"ff": 2048, "limit": 7.0}}
+    giforax = {"architecture": "Giforax", "vocab": DESIGN_VOCAB, "width": DESIGN_WIDTH, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
+               "layers": [{"type": "attention", "mixer": sigmoid, "mlp": gated},
+                          {"type": "attention", "mixer": dict(sigmoid, kv_from=0), "mlp": gated},
+                          {"type": "mingru", "mixer": {"width": DESIGN_WIDTH}, "mlp": gated},
+                          {"type": "attention", "mixer": sigmoid, "mlp": gated}]}
+    return {"zipedra": zipedra, "giforax": giforax, "llama": llama}
 
 
 def run_design(args) -> dict:
-    """Prefill and decode throughput of the Zipedra design at layer sizes that resemble a real model's, beside the
+    """Prefill and decode throughput of the design ``args.design`` at layer sizes that resemble a real model's, beside the
     closest Llama of equal width, and its own kernels alone beside the like kernels of Llama, each against the roofline."""
     import contextlib
     import io
@@ -453,6 +463,8 @@ def run_design(args) -> dict:
     points = {}
     with torch.inference_mode():
         for name, config in design_configs().items():
+            if name not in (args.design, "llama"):
+                continue
             model = random_model(config, seed=0, dtype="bfloat16")
             runner = make_runner(model, page_size=PAGE_SIZE, max_tokens=(batch + 1) * (prompt_len + 256), max_requests=batch + 1,
                                  max_request_tokens=prompt_len + 256, check_errors=False)
@@ -490,11 +502,14 @@ def run_design(args) -> dict:
             torch.cuda.empty_cache()
         lines = io.StringIO()
         with contextlib.redirect_stdout(lines):
-            for argv in (["latent-attention"], ["prefill-attention", "--heads", "16", "--kv-heads", "8"],
-                         ["decode-attention", "--heads", "16", "--kv-heads", "8"], ["linear-attention"], ["expert-product"]):
+            own = {"zipedra": (["latent-attention"], ["linear-attention"], ["expert-product"]),
+                   "giforax": (["sigmoid-attention"], ["sigmoid-attention", "--chunk", "2048"], ["gated-recurrence"], ["layer-tails"],
+                               ["expert-product"])}[args.design]
+            for argv in (*own, ["prefill-attention", "--heads", "16", "--kv-heads", "8"],
+                         ["decode-attention", "--heads", "16", "--kv-heads", "8"]):
                 bench_kernels.main(argv)
     kernels = [json.loads(line) for line in lines.getvalue().splitlines() if line.startswith("{")]
-    return {"design": "zipedra", "beside": "llama", "dtype": "bf16", "data": "synthetic token ids, random weights",
+    return {"design": args.design, "beside": "llama", "dtype": "bf16", "data": "synthetic token ids, random weights",
             "config": {"width": DESIGN_WIDTH, "heads": DESIGN_HEADS, "layer_runs": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
                        "prompt_len": prompt_len, "batch": batch, "decode_steps": steps, "page_size": PAGE_SIZE},
             "points": points, "kernels": kernels}
@@ -596,7 +611,7 @@ def main(argv=None) -> int:
     parser.add_argument("--gemm-backend", choices=["auto", "tcgen05", "library"], default="auto")
     parser.add_argument("--workloads", nargs="*", default=list(WORKLOADS), choices=list(WORKLOADS),
                         help="serving workloads of the smaller sizes to add to points")
-    parser.add_argument("--design", choices=["zipedra"], default=None,
+    parser.add_argument("--design", choices=["zipedra", "giforax"], default=None,
                         help="instead of the headline run: prefill and decode throughput of this design at layer sizes that "
                              "resemble a real model's, beside the closest Llama, and its kernels against the roofline")
     args = parser.parse_args(argv)

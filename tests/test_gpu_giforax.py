@@ -463,6 +463,66 @@ def test_layer_norm_and_the_tails_of_sublayers(width, rows):
         assert (normed.cpu().double() - want_out).abs().max() <= tol * want_out.abs().max()
 
 
+# ------------------------------------------------- the two attention kernels
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,chunk,page", [(6, 2, 64, 64, 200, 16), (16, 8, 128, 128, 512, 16), (3, 1, 40, 24, 7, 8),
+                                                             (4, 4, 72, 128, 64, 32), (5, 1, 16, 8, 0, 4), (70, 1, 32, 32, 129, 16)])
+def test_sigmoid_attention_kernels_agree_with_plain_arithmetic(heads, kv_heads, dim, vdim, chunk, page):
+    """The tensor-core kernel and the CUDA-core kernel on the same bf16 pages, against float64: a ragged step (prompt
+    portions that begin and end off the 64-key tile edges and the chunk edges, beside single tokens) and a step of single
+    tokens with contexts just below, at and above tile, page and chunk edges.  Unwritten cache holds NaN."""
+    need_gpu()
+    from torchinferno_b200.kernels import ops
+    g = torch.Generator().manual_seed(heads * dim + chunk)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=CUDA)
+    c = chunk or 10 ** 6
+    cases = {"ragged": [(0, 70), (63, 2), (64, 1), (100, 129), (5, 1), (c - 1 if chunk else 30, 3)],
+             "single": [(0, 1), (62, 1), (63, 1), (64, 1), (127, 1), (300, 1), (c - 1 if chunk else 511, 1), (c if chunk else 512, 1), (2 * c + 1 if chunk else 77, 1)]}
+    group = heads // kv_heads
+    for name, entries in cases.items():
+        entries = [(s, n) for s, n in entries if s + n <= 1200]
+        pages_per = max(-(-(start + n) // page) for start, n in entries)
+        total = len(entries) * pages_per
+        keys = torch.full((total, kv_heads, page, dim), float("nan")).to(torch.bfloat16)
+        values = torch.full((total, kv_heads, page, vdim), float("nan")).to(torch.bfloat16)
+        table = torch.randperm(total, generator=g).to(torch.int32).view(len(entries), pages_per)
+        n_tokens = sum(n for _, n in entries)
+        q = torch.randn(n_tokens, heads, dim, generator=g).to(torch.bfloat16)
+        gate = torch.randn(n_tokens, heads + 3, generator=g).to(torch.bfloat16)
+        bias = torch.randn(heads, generator=g)
+        q_start = [0]
+        for _, n in entries:
+            q_start.append(q_start[-1] + n)
+        want = torch.empty(n_tokens, heads, vdim, dtype=torch.float64)
+        for e, (start, n) in enumerate(entries):
+            ctx = start + n
+            pos = torch.arange(ctx)
+            krows = torch.randn(ctx, kv_heads, dim, generator=g).to(torch.bfloat16)
+            vrows = torch.randn(ctx, kv_heads, vdim, generator=g).to(torch.bfloat16)
+            keys[table[e][pos // page].long(), :, pos % page] = krows
+            values[table[e][pos // page].long(), :, pos % page] = vrows
+            qpos = start + torch.arange(n)
+            seen = (pos[None, :] <= qpos[:, None]) & ((pos[None, :] // c) == (qpos[:, None] // c))
+            qe = q[q_start[e]:q_start[e + 1]].double()
+            for h in range(heads):
+                score = qe[:, h] @ krows[:, h // group].double().T * 0.11 + bias[h].double()
+                weight = torch.sigmoid(score) * seen
+                want[q_start[e]:q_start[e + 1], h] = (weight @ vrows[:, h // group].double()) \
+                    * torch.sigmoid(gate[q_start[e]:q_start[e + 1], h].double())[:, None]
+        pool = torch.cat([keys.flatten(1), values.flatten(1)], dim=1).cuda().contiguous()
+        kview = pool[:, :kv_heads * page * dim].unflatten(1, (kv_heads, page, dim))
+        vview = pool[:, kv_heads * page * dim:].unflatten(1, (kv_heads, page, vdim))
+        for simt in (False, True):
+            out = torch.empty(n_tokens, heads * vdim, dtype=torch.bfloat16, device=CUDA)
+            ops.sigmoid_attention(q.view(n_tokens, heads * dim).cuda(), kview, vview, out, i32(q_start), i32([s for s, _ in entries]),
+                                  i32(list(range(len(entries)))), table.cuda().contiguous(), len(entries), max(n for _, n in entries),
+                                  heads, kv_heads, scale=0.11, chunk=chunk, head_bias=bias.cuda(), gate=gate.cuda()[:, :heads],
+                                  force_simt=simt)
+            got = out.view(n_tokens, heads, vdim).cpu().double()
+            assert torch.isfinite(got).all(), f"{name}, simt={simt}"
+            err = (got - want).abs().max()
+            assert err <= 6e-3 * want.abs().max(), f"{name}, simt={simt}: {err:.3e} of {want.abs().max():.3e}"
+
+
 # ------------------------------------------------ entry point and programs
 def test_greedy_generation_through_the_engine_and_its_scheduler(folders):
     need_gpu()

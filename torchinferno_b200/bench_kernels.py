@@ -8,6 +8,9 @@
     python -m torchinferno_b200.bench_kernels latent-attention --tokens 2048 --batch 8 --context 2048
     python -m torchinferno_b200.bench_kernels linear-attention --tokens 2048 --batch 8
     python -m torchinferno_b200.bench_kernels expert-product --tokens 2048
+    python -m torchinferno_b200.bench_kernels sigmoid-attention --tokens 2048 --batch 8 --context 2048 --chunk 512
+    python -m torchinferno_b200.bench_kernels gated-recurrence --tokens 2048 --batch 8
+    python -m torchinferno_b200.bench_kernels layer-tails --rows 2048
 
 Each run prints one JSON line per case: microseconds (median of CUDA-event timings, an L2 flush
 between iterations), the bytes or flops the kernel has to move or do, and the fraction of the
@@ -325,8 +328,85 @@ def run_expert_product(args) -> None:
            flops=flops, tokens=t, experts=e, top=top, hidden=w, expert_size=ff)
     report("expert_product[down]", timer(lambda: ops.moe_expert_product(inner, down, outer, offsets, order, top, x_by_pair=False)),
            flops=flops, tokens=t, experts=e, top=top, hidden=w, expert_size=ff)
+    gate_up = (torch.randn(e, 2 * ff, w, device="cuda") * 0.02).to(torch.bfloat16)
+    scale = torch.rand(t * top, device="cuda")
+    report("expert_product[gate and up, clamped gated unit, row scale]",
+           timer(lambda: ops.moe_expert_product(x, gate_up, inner, offsets, order, top, x_by_pair=True, act="glu_clamp", limit=7.0,
+                                                alpha=1.702, row_scale=scale)),
+           flops=2 * flops, tokens=t, experts=e, top=top, hidden=w, expert_size=ff)
     dense = LinearWeight((torch.randn(top * ff, w, device="cuda") * 0.02).to(torch.bfloat16), few_rows_tcgen05=False)
     report("linear[dense, the same flops]", timer(lambda: linear(x, dense)), flops=flops, tokens=t, hidden=w, out=top * ff)
+
+
+def run_sigmoid_attention(args) -> None:
+    """The attention with sigmoid weights inside chunks on a prompt of --tokens (flops: both products over the keys a query
+    sees) and on --batch single tokens at --context (bytes: the keys and values of the chunk each context ends in)."""
+    h, k, d, v, page, chunk = args.heads, args.kv_heads, args.head_dim, args.value_dim, args.page_size, args.chunk
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    timer = Timer(args.iters)
+    for mode in ("prompt", "single tokens"):
+        n_entries, ctx = (1, args.tokens) if mode == "prompt" else (args.batch, args.context)
+        pages_per = -(-ctx // page)
+        pool = (torch.randn(n_entries * pages_per, k * page * (d + v), device="cuda") * 0.5).to(torch.bfloat16)
+        keys = pool[:, :k * page * d].unflatten(1, (k, page, d))
+        values = pool[:, k * page * d:].unflatten(1, (k, page, v))
+        table = torch.randperm(n_entries * pages_per, device="cuda", dtype=torch.int32).view(n_entries, pages_per).contiguous()
+        n = ctx if mode == "prompt" else n_entries
+        q = torch.randn(n, h * d, device="cuda").to(torch.bfloat16)
+        gate = torch.randn(n, h, device="cuda").to(torch.bfloat16)
+        bias = torch.zeros(h, device="cuda")
+        out = torch.empty(n, h * v, dtype=torch.bfloat16, device="cuda")
+        seen = lambda p: p - (p // chunk) * chunk + 1 if chunk else p + 1
+        if mode == "prompt":
+            q_start, kv_start, slots, max_q = i32([0, n]), i32([0]), i32([0]), n
+            flops, moved = 2 * h * (d + v) * sum(seen(p) for p in range(ctx)), None
+        else:
+            q_start, kv_start, slots, max_q = i32(list(range(n + 1))), i32([ctx - 1] * n), i32(list(range(n))), 1
+            flops, moved = None, n * seen(ctx - 1) * k * (d + v) * 2
+        for simt in (False, True):
+            fn = lambda: ops.sigmoid_attention(q, keys, values, out, q_start, kv_start, slots, table, n_entries, max_q, h, k,
+                                               scale=0.1, chunk=chunk, head_bias=bias, gate=gate, force_simt=simt)
+            report(f"sigmoid_attention[{'cuda cores' if simt else 'mma.sync'}, {mode}]", timer(fn), flops=flops, bytes_moved=moved,
+                   entries=n_entries, context=ctx, heads=h, kv_heads=k, head_dim=d, value_dim=v, chunk=chunk)
+
+
+def run_gated_recurrence(args) -> None:
+    """The element-wise gated recurrence on a prompt of --tokens and on --batch single tokens (bytes: the three projections
+    read, the rows written, the state read and written)."""
+    w = args.width
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    timer = Timer(args.iters)
+    for mode in ("prompt", "single tokens"):
+        n_entries, n = (1, args.tokens) if mode == "prompt" else (args.batch, args.batch)
+        proj = torch.randn(n, 3 * w, device="cuda").to(torch.bfloat16)
+        out = torch.empty(n, w, dtype=torch.bfloat16, device="cuda")
+        state = torch.zeros(n_entries, w, device="cuda")
+        bias = torch.zeros(w, device="cuda")
+        q_start = i32([0, n]) if mode == "prompt" else i32(list(range(n + 1)))
+        slots = i32(list(range(n_entries)))
+        max_q = n if mode == "prompt" else 1
+        fn = lambda: ops.gated_recurrence(proj, 0, w, 2 * w, bias, bias, state, q_start, slots, out, n_entries, max_q)
+        report(f"gated_recurrence[{mode}]", timer(fn), bytes_moved=n * w * 8 + n_entries * w * 8, tokens=n, width=w)
+
+
+def run_layer_tails(args) -> None:
+    """The launches around a sublayer of a block with norms on both sides: the layer norm of the residual, and the tail
+    (norm of the sublayer's output, sum, depth average over --depth earlier outputs, the next norm), beside the RMS
+    norm with its fused sum (bytes: what each has to read and write)."""
+    rows, w, depth = args.rows, args.hidden, args.depth
+    timer = Timer(args.iters)
+    history = torch.randn(depth + 1, rows, w, device="cuda")
+    y = torch.randn(rows, w, device="cuda").to(torch.bfloat16)
+    out = torch.empty(rows, w, dtype=torch.bfloat16, device="cuda")
+    wt, b, coef = torch.ones(w, device="cuda"), torch.zeros(w, device="cuda"), torch.ones(depth, device="cuda")
+    report("layernorm", timer(lambda: ops.layernorm(history[0], wt, b, 1e-6, out)), bytes_moved=rows * w * 6, rows=rows, hidden=w)
+    report("layernorm_tail[norm, sum, norm]", timer(lambda: ops.layernorm_tail(history[0], 1e-6, y=y, y_norm=(wt, b), out=out, out_norm=(wt, b))),
+           bytes_moved=rows * w * 12, rows=rows, hidden=w)
+    report("layernorm_tail[norm, sum, depth average]",
+           timer(lambda: ops.layernorm_tail(history[depth - 1], 1e-6, y=y, y_norm=(wt, b), history=history, coef=coef, count=depth)),
+           bytes_moved=rows * w * (2 + 8 + 4 * depth), rows=rows, hidden=w, depth=depth)
+    delta = torch.randn(rows, w, device="cuda").to(torch.bfloat16)
+    report("add_rmsnorm", timer(lambda: ops.add_rmsnorm(delta, history[0], wt, 1e-6, out)), bytes_moved=rows * w * 12, rows=rows, hidden=w)
 
 
 def main(argv=None) -> int:
@@ -405,6 +485,30 @@ def main(argv=None) -> int:
     p.add_argument("--expert-size", type=int, default=1024)
     p.add_argument("--iters", type=int, default=10)
     p.set_defaults(func=run_expert_product)
+    p = sub.add_parser("sigmoid-attention")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--value-dim", type=int, default=128)
+    p.add_argument("--chunk", type=int, default=512)
+    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_sigmoid_attention)
+    p = sub.add_parser("gated-recurrence")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--width", type=int, default=2048)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_gated_recurrence)
+    p = sub.add_parser("layer-tails")
+    p.add_argument("--rows", type=int, default=2048)
+    p.add_argument("--hidden", type=int, default=2048)
+    p.add_argument("--depth", type=int, default=5)
+    p.add_argument("--iters", type=int, default=10)
+    p.set_defaults(func=run_layer_tails)
     args = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_kernels needs a CUDA device")

@@ -261,6 +261,237 @@ static int launch_sigmoid_simt(const void* q, const void* k_pages, const void* v
   return TIB_OK;
 }
 
+
+// ------------------------------------------------------------ tensor cores
+// 64 rows (tokens x the query heads of one kv head) against tiles of 64 keys that are aligned to absolute positions,
+// four warps of 16 rows.  Keys and values of a tile come in by cp.async, row by row from their pages, two stages.
+// A row's sum runs over the tiles in rising order and every key has a fixed place in its tile, so the result
+// does not depend on how the prompt was cut or on what else the step holds.  Rows of values past the last position
+// of the tile are zero-filled (unwritten cache may hold anything); so are the padding columns up to DK / DV.
+constexpr int kSmRows = 64, kSmKeys = 64, kSmThreads = 128;
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(kSmThreads)
+sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                             const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, SigAttnArgs a,
+                             int group_chunk, int q_tile) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int KP = DK + 8, VP = DV + 8;        // padded rows: ldmatrix rows fall in different banks
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(sm_raw);          // [64][KP]
+  __nv_bfloat16* k_s = q_s + kSmRows * KP;                                 // [2][64][KP]
+  __nv_bfloat16* v_s = k_s + 2 * kSmKeys * KP;                             // [2][64][VP]
+  __shared__ int key_page[2][kSmKeys];
+
+  const int d = a.dim, vd = a.vdim;
+  const int entry = blockIdx.y;
+  const int group = a.heads / a.kv_heads;
+  const int chunks = (group + group_chunk - 1) / group_chunk;
+  const int kvh = blockIdx.z / chunks;
+  const int g0 = (blockIdx.z - kvh * chunks) * group_chunk;
+  const int gc = min(group_chunk, group - g0);
+  const int row0 = a.q_start[entry];
+  const int q_len = a.q_start[entry + 1] - row0;
+  const int t0 = blockIdx.x * q_tile;
+  if (t0 >= q_len) return;
+  const int nt = min(q_tile, q_len - t0);
+  const int nrows = nt * gc;
+  const int pos0 = a.kv_start[entry] + t0;
+  const int last_pos = pos0 + nt - 1;
+  const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int first_key = first_visible(pos0, a.chunk, a.window);
+  const int b_lo = first_key / kSmKeys, b_hi = last_pos / kSmKeys;
+
+  auto fetch = [&](int stage, int b) {
+    // the page of every key of the tile, once
+    if (tid < kSmKeys) {
+      const int kp = b * kSmKeys + tid;
+      int page = -1;
+      if (kp <= last_pos && kp >= first_key) {
+        page = table[kp / a.page_size];
+        if (page < 0 || page >= a.num_pages) {
+          if (a.error_word) atomicExch(a.error_word, 0x10000 + entry);
+          page = -1;
+        }
+      }
+      key_page[stage][tid] = page;
+    }
+    __syncthreads();
+    constexpr int KPIECES = DK / 8, VPIECES = DV / 8;
+    for (int e = tid; e < kSmKeys * KPIECES; e += kSmThreads) {
+      const int j = e / KPIECES, c = (e - j * KPIECES) * 8;
+      const int page = key_page[stage][j];
+      const bool ok = page >= 0 && c < d;
+      const int kp = b * kSmKeys + j;
+      const __nv_bfloat16* src = k_pages + (size_t)max(page, 0) * a.page_stride + ((size_t)kvh * a.page_size + (kp % a.page_size)) * d + (ok ? c : 0);
+      cp_async16(k_s + ((size_t)stage * kSmKeys + j) * KP + c, src, ok);
+    }
+    for (int e = tid; e < kSmKeys * VPIECES; e += kSmThreads) {
+      const int j = e / VPIECES, c = (e - j * VPIECES) * 8;
+      const int page = key_page[stage][j];
+      const bool ok = page >= 0 && c < vd;
+      const int kp = b * kSmKeys + j;
+      const __nv_bfloat16* src = v_pages + (size_t)max(page, 0) * a.page_stride + ((size_t)kvh * a.page_size + (kp % a.page_size)) * vd + (ok ? c : 0);
+      cp_async16(v_s + ((size_t)stage * kSmKeys + j) * VP + c, src, ok);
+    }
+    cp_async_commit();
+  };
+
+  // queries: 16-byte pieces, rows past the tile's end and padding columns are zero
+  {
+    constexpr int QPIECES = DK / 8;
+    for (int e = tid; e < kSmRows * QPIECES; e += kSmThreads) {
+      const int r = e / QPIECES, c = (e - r * QPIECES) * 8;
+      const bool ok = r < nrows && c < d;
+      const int t = ok ? r / gc : 0, g = ok ? r - t * gc : 0;
+      const __nv_bfloat16* src = q + (size_t)(row0 + t0 + t) * a.heads * d + (size_t)(kvh * group + g0 + g) * d + (ok ? c : 0);
+      cp_async16(q_s + (size_t)r * KP + c, src, ok);
+    }
+  }
+  fetch(0, b_lo);
+
+  // this thread's two rows: g8 and g8 + 8 of the warp's sixteen
+  const int g8 = lane >> 2, t4 = lane & 3;
+  int qpos[2], lo[2];
+  float bias[2];
+  bool live[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g8 + 8 * h;
+    live[h] = r < nrows;
+    const int t = live[h] ? r / gc : 0, g = live[h] ? r - t * gc : 0;
+    qpos[h] = pos0 + t;
+    lo[h] = first_visible(qpos[h], a.chunk, a.window);
+    bias[h] = a.head_bias ? a.head_bias[kvh * group + g0 + g] : 0.f;
+  }
+  float o[DV / 8][4];
+#pragma unroll
+  for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  for (int b = b_lo; b <= b_hi; ++b) {
+    const int stage = (b - b_lo) & 1;
+    if (b < b_hi) {
+      fetch(stage ^ 1, b + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    // (a warp whose rows see nothing of this tile still passes the barriers)
+    const int warp_first = pos0 + (warp * 16) / gc, warp_last = pos0 + min(nrows - 1, warp * 16 + 15) / gc;
+    const bool any = warp * 16 < nrows && b * kSmKeys <= warp_last &&
+                     b * kSmKeys + kSmKeys - 1 >= first_visible(warp_first, a.chunk, a.window);
+    if (any) {
+      const __nv_bfloat16* kt = k_s + (size_t)stage * kSmKeys * KP;
+      const __nv_bfloat16* vt = v_s + (size_t)stage * kSmKeys * VP;
+      float s[kSmKeys / 8][4];
+#pragma unroll
+      for (int n = 0; n < kSmKeys / 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DK; kk += 16) {
+        uint32_t af[4];
+        ldmatrix_x4(af, q_s + (size_t)(warp * 16 + (lane & 15)) * KP + kk + (lane >> 4) * 8);
+#pragma unroll
+        for (int j = 0; j < kSmKeys / 16; ++j) {
+          uint32_t bf[4];
+          ldmatrix_x4(bf, kt + (size_t)(j * 16 + ((lane >> 4) << 3) + (lane & 7)) * KP + kk + ((lane >> 3) & 1) * 8);
+          mma_bf16(s[2 * j], af, bf[0], bf[1]);
+          mma_bf16(s[2 * j + 1], af, bf[2], bf[3]);
+        }
+      }
+      // weights in fp32; into the second product as a high bf16 part and the remainder
+      uint32_t p_hi[kSmKeys / 16][4], p_lo[kSmKeys / 16][4];
+#pragma unroll
+      for (int n = 0; n < kSmKeys / 8; ++n) {
+        float w[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int h = c >> 1;
+          const int kp = b * kSmKeys + n * 8 + 2 * t4 + (c & 1);
+          const bool allowed = live[h] && kp <= qpos[h] && kp >= lo[h];
+          w[c] = allowed ? __fdividef(1.f, 1.f + __expf(-(s[n][c] * a.scale + bias[h]))) : 0.f;
+        }
+        const int kk = n >> 1, half = (n & 1) * 2;
+        const __nv_bfloat162 h01 = __floats2bfloat162_rn(w[0], w[1]), h23 = __floats2bfloat162_rn(w[2], w[3]);
+        p_hi[kk][half] = *reinterpret_cast<const uint32_t*>(&h01);
+        p_hi[kk][half + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+        const float2 f01 = bf16x2_floats(h01), f23 = bf16x2_floats(h23);
+        p_lo[kk][half] = pack_bf16(w[0] - f01.x, w[1] - f01.y);
+        p_lo[kk][half + 1] = pack_bf16(w[2] - f23.x, w[3] - f23.y);
+      }
+#pragma unroll
+      for (int kk = 0; kk < kSmKeys / 16; ++kk) {
+#pragma unroll
+        for (int dn = 0; dn < DV / 16; ++dn) {
+          uint32_t bv[4];
+          ldmatrix_x4_trans(bv, vt + (size_t)(kk * 16 + (lane & 15)) * VP + dn * 16 + ((lane >> 4) << 3));
+          mma_bf16(o[2 * dn], p_hi[kk], bv[0], bv[1]);
+          mma_bf16(o[2 * dn + 1], p_hi[kk], bv[2], bv[3]);
+          mma_bf16(o[2 * dn], p_lo[kk], bv[0], bv[1]);
+          mma_bf16(o[2 * dn + 1], p_lo[kk], bv[2], bv[3]);
+        }
+      }
+    }
+    __syncthreads();      // the stage is free for the fetch after next
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!live[h]) continue;
+    const int r = warp * 16 + g8 + 8 * h;
+    const int t = r / gc, g = r - t * gc;
+    const int head = kvh * group + g0 + g;
+    const size_t tok = (size_t)(row0 + t0 + t);
+    float gate = 1.f;
+    if (a.gate) {
+      const float z = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[tok * a.ld_gate + head]
+                                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gate)[tok * a.ld_gate + head]);
+      gate = sig_f(z);
+    }
+    __nv_bfloat16* dst = out + tok * a.heads * vd + (size_t)head * vd;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+      const int col = n * 8 + 2 * t4;
+      if (col + 1 < vd)
+        *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(o[n][2 * h] * gate, o[n][2 * h + 1] * gate);
+      else if (col < vd)
+        dst[col] = __float2bfloat16_rn(o[n][2 * h] * gate);
+    }
+  }
+}
+
+template <int DK, int DV>
+static int launch_sigmoid_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const SigAttnArgs& a,
+                              int n_entries, int max_q_len, cudaStream_t stream) {
+  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)kSmRows * (DK + 8) + 2 * (size_t)kSmKeys * (DK + 8) + 2 * (size_t)kSmKeys * (DV + 8));
+  auto kern = sigmoid_attention_mma_kernel<DK, DV>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int group = a.heads / a.kv_heads;
+  const int group_chunk = group < kSmRows ? group : kSmRows;
+  const int q_tile = kSmRows / group_chunk;
+  const int chunks = (group + group_chunk - 1) / group_chunk;
+  if ((int64_t)a.kv_heads * chunks > 65535) return TIB_E_SIZE;
+  dim3 grid(ceil_div(max_q_len, q_tile), n_entries, a.kv_heads * chunks);
+  TIB_LAUNCH_DEPENDENT(kern, grid, kSmThreads, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
+                       (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, a, group_chunk, q_tile);
+  return TIB_OK;
+}
+
+// Whether the tensor-core kernel takes these head sizes (bf16; rows of 16-byte pieces).
+static bool sigmoid_mma_takes(int dim, int vdim, int64_t page_stride, const void* q, const void* k_pages, const void* v_pages) {
+  return dim % 8 == 0 && vdim % 8 == 0 && dim <= 128 && vdim <= 128 && page_stride % 8 == 0 &&
+         (((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+}
+
 }  // namespace tib
 
 using namespace tib;
@@ -297,13 +528,14 @@ TIB_API int tib_qk_norm_append(const void* proj, int64_t ld, int q_off, int k_of
 }
 
 // q: [n_tokens, heads * dim]; out: [n_tokens, heads * vdim]; gate: [n_tokens, >= heads] logits (row stride ld_gate)
-// or null; head_bias: [heads] fp32 or null.
+// or null; head_bias: [heads] fp32 or null.  bf16 with head sizes that are multiples of 8 up to 128 runs on the tensor
+// cores unless force_simt.
 TIB_API int tib_sigmoid_attention(const void* q, const void* k_pages, const void* v_pages, void* out, const int* q_start,
                                   const int* kv_start, const int* slots, const int* block_table, int table_stride,
                                   int n_entries, int max_q_len, int heads, int kv_heads, int dim, int vdim, int page_size,
                                   int64_t page_stride, int num_pages, int chunk, int window, float scale,
                                   const float* head_bias, const void* gate, int gate_dtype, int64_t ld_gate, int* error_word,
-                                  int dtype, cudaStream_t stream) {
+                                  int dtype, int force_simt, cudaStream_t stream) {
   if (n_entries == 0 || max_q_len == 0) return TIB_OK;
   if (!q || !k_pages || !v_pages || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
   if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || vdim < 1 || page_size < 1 || chunk < 0 || window < 0)
@@ -314,6 +546,12 @@ TIB_API int tib_sigmoid_attention(const void* q, const void* k_pages, const void
   a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.page_size = page_size; a.page_stride = page_stride;
   a.num_pages = num_pages; a.chunk = chunk; a.window = window; a.scale = scale; a.head_bias = head_bias; a.gate = gate;
   a.gate_dtype = gate_dtype; a.ld_gate = ld_gate; a.error_word = error_word;
+  if (dtype == TIB_BF16 && !force_simt && sigmoid_mma_takes(dim, vdim, page_stride, q, k_pages, v_pages)) {
+    if (dim <= 64 && vdim <= 64) return launch_sigmoid_mma<64, 64>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
+    if (dim <= 64) return launch_sigmoid_mma<64, 128>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
+    if (vdim <= 64) return launch_sigmoid_mma<128, 64>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
+    return launch_sigmoid_mma<128, 128>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
+  }
   const int vpl = (vdim + 31) / 32;
 #define TIB_SA_DISPATCH(T)                                                                                   \
   (vpl <= 1 ? launch_sigmoid_simt<T, 1>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream)           \

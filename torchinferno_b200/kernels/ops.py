@@ -1111,10 +1111,11 @@ def sigmoid_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor,
                       kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int, max_q_len: int,
                       heads: int, kv_heads: int, *, scale: float, chunk: int = 0, window: int = 0,
                       head_bias: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-                      error_word: torch.Tensor | None = None) -> torch.Tensor:
+                      error_word: torch.Tensor | None = None, force_simt: bool = False) -> torch.Tensor:
     """out[i] = sigmoid(gate[i]) * sum over visible j of sigmoid(q_i . k_j * scale + head_bias) * v_j, per head; visible:
     j <= i, in i's chunk of ``chunk`` positions (0: no chunks) and within ``window`` (0: none).  ``gate``: [tokens, heads]
-    logits (a column slice is fine) or None."""
+    logits (a column slice is fine) or None.  bfloat16 with head sizes that are multiples of 8 up to 128 runs on the tensor
+    cores, everything else (and ``force_simt``) on the CUDA-core kernel."""
     _need(q, "q"), _need(out, "out", q.dtype)
     dim, vdim, page_size = keys.shape[3], values.shape[3], keys.shape[2]
     n = q.shape[0]
@@ -1131,7 +1132,8 @@ def sigmoid_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor,
         c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
         c_int(page_size), c_int64(keys.stride(0)), c_int(keys.shape[0]), c_int(chunk), c_int(window), c_float(scale),
         _ptr(head_bias), _ptr(gate), c_int(_code(gate.dtype) if gate is not None else 0),
-        c_int64(gate.stride(0) if gate is not None else 0), _ptr(error_word), c_int(_code(q.dtype)), _stream()))
+        c_int64(gate.stride(0) if gate is not None else 0), _ptr(error_word), c_int(_code(q.dtype)), c_int(int(force_simt)),
+        _stream()))
     return out
 
 
