@@ -511,16 +511,17 @@ def test_sigmoid_attention_kernels_agree_with_plain_arithmetic(heads, kv_heads, 
         pool = torch.cat([keys.flatten(1), values.flatten(1)], dim=1).cuda().contiguous()
         kview = pool[:, :kv_heads * page * dim].unflatten(1, (kv_heads, page, dim))
         vview = pool[:, kv_heads * page * dim:].unflatten(1, (kv_heads, page, vdim))
-        for simt in (False, True):
+        # (single tokens on the tensor cores: also with the keys of a context shared out over 1, 3 and 7 blocks)
+        for simt, splits in ((False, None), (True, None)) + (((False, 1), (False, 3), (False, 7)) if name == "single" else ()):
             out = torch.empty(n_tokens, heads * vdim, dtype=torch.bfloat16, device=CUDA)
             ops.sigmoid_attention(q.view(n_tokens, heads * dim).cuda(), kview, vview, out, i32(q_start), i32([s for s, _ in entries]),
                                   i32(list(range(len(entries)))), table.cuda().contiguous(), len(entries), max(n for _, n in entries),
                                   heads, kv_heads, scale=0.11, chunk=chunk, head_bias=bias.cuda(), gate=gate.cuda()[:, :heads],
-                                  force_simt=simt)
+                                  force_simt=simt, max_kv_len=max(s + n for s, n in entries), splits=splits)
             got = out.view(n_tokens, heads, vdim).cpu().double()
-            assert torch.isfinite(got).all(), f"{name}, simt={simt}"
+            assert torch.isfinite(got).all(), f"{name}, simt={simt}, splits={splits}"
             err = (got - want).abs().max()
-            assert err <= 6e-3 * want.abs().max(), f"{name}, simt={simt}: {err:.3e} of {want.abs().max():.3e}"
+            assert err <= 6e-3 * want.abs().max(), f"{name}, simt={simt}, splits={splits}: {err:.3e} of {want.abs().max():.3e}"
 
 
 # ------------------------------------------------ entry point and programs

@@ -29,6 +29,8 @@ struct GruArgs {
   int width, run_len, max_runs;
 };
 
+constexpr int kGruAhead = 8;      // tokens whose gates are computed ahead of the serial chain
+
 __device__ __forceinline__ float gru_load(const void* p, int dtype, size_t i) {
   return dtype == TIB_F32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
@@ -53,11 +55,18 @@ __global__ void __launch_bounds__(128) gated_recurrence_fold_kernel(GruArgs a) {
     a.run_b[((size_t)entry * a.max_runs + last_run) * a.width + c] = a.state[(size_t)a.slots[entry] * a.width + c];
   const float bz = a.bias_z ? a.bias_z[c] : 0.f, bu = a.bias_u ? a.bias_u[c] : 0.f;
   float A = 1.f, B = 0.f;
-  for (int t = t0; t < t0 + a.run_len; ++t) {
-    float z, cand;
-    gru_gates(a, (size_t)(row0 + t), c, bz, bu, z, cand);
-    A *= (1.f - z);
-    B = fmaf(1.f - z, B, z * cand);
+  for (int t = t0; t < t0 + a.run_len; t += kGruAhead) {
+    // (the gates of several tokens are made side by side; only the two products a token are a chain)
+    float z[kGruAhead], cand[kGruAhead];
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i)
+      if (t + i < t0 + a.run_len) gru_gates(a, (size_t)(row0 + t + i), c, bz, bu, z[i], cand[i]);
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i) {
+      if (t + i >= t0 + a.run_len) break;
+      A *= (1.f - z[i]);
+      B = fmaf(1.f - z[i], B, z[i] * cand[i]);
+    }
   }
   const size_t at = ((size_t)entry * a.max_runs + run) * a.width + c;
   a.run_a[at] = A;
@@ -81,18 +90,28 @@ __global__ void __launch_bounds__(128) gated_recurrence_scan_kernel(GruArgs a) {
     const size_t at = ((size_t)entry * a.max_runs + r) * a.width + c;
     S = fmaf(a.run_a[at], S, a.run_b[at]);
   }
-  for (int t = t0; t < t1; ++t) {
-    const size_t row = (size_t)(row0 + t);
-    float z, cand;
-    gru_gates(a, row, c, bz, bu, z, cand);
-    S = fmaf(1.f - z, S, z * cand);
-    float o = S;
-    if (a.g_off >= 0) {
-      const float g = gru_load(a.proj, a.dtype, row * a.ld + a.g_off + c);
-      o *= g / (1.f + expf(-g));
+  for (int t = t0; t < t1; t += kGruAhead) {
+    float z[kGruAhead], cand[kGruAhead], gate[kGruAhead];
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i) {
+      if (t + i >= t1) continue;
+      const size_t row = (size_t)(row0 + t + i);
+      gru_gates(a, row, c, bz, bu, z[i], cand[i]);
+      gate[i] = 1.f;
+      if (a.g_off >= 0) {
+        const float g = gru_load(a.proj, a.dtype, row * a.ld + a.g_off + c);
+        gate[i] = g / (1.f + expf(-g));
+      }
     }
-    if (a.out_dtype == TIB_F32) reinterpret_cast<float*>(a.out)[row * a.width + c] = o;
-    else reinterpret_cast<__nv_bfloat16*>(a.out)[row * a.width + c] = __float2bfloat16_rn(o);
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i) {
+      if (t + i >= t1) break;
+      const size_t row = (size_t)(row0 + t + i);
+      S = fmaf(1.f - z[i], S, z[i] * cand[i]);
+      const float o = S * gate[i];
+      if (a.out_dtype == TIB_F32) reinterpret_cast<float*>(a.out)[row * a.width + c] = o;
+      else reinterpret_cast<__nv_bfloat16*>(a.out)[row * a.width + c] = __float2bfloat16_rn(o);
+    }
   }
   if (t1 == len) slot[c] = S;
 }

@@ -274,7 +274,9 @@ template <int DK, int DV>
 __global__ void __launch_bounds__(kSmThreads)
 sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                              const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, SigAttnArgs a,
-                             int group_chunk, int q_tile) {
+                             int group_chunk, int q_tile, int splits, float* __restrict__ partial) {
+  // splits > 0: a step of single tokens.  blockIdx.x is then a share of the key tiles instead of a query tile, and the
+  // sums of that share leave ungated in fp32, partial[split][token][head][vdim], for sigmoid_attention_sum_kernel.
   pdl_wait();
   pdl_trigger();
   constexpr int KP = DK + 8, VP = DV + 8;        // padded rows: ldmatrix rows fall in different banks
@@ -293,7 +295,7 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   const int gc = min(group_chunk, group - g0);
   const int row0 = a.q_start[entry];
   const int q_len = a.q_start[entry + 1] - row0;
-  const int t0 = blockIdx.x * q_tile;
+  const int t0 = splits > 0 ? 0 : blockIdx.x * q_tile;
   if (t0 >= q_len) return;
   const int nt = min(q_tile, q_len - t0);
   const int nrows = nt * gc;
@@ -302,7 +304,12 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   const int* table = a.block_table + (size_t)a.slots[entry] * a.table_stride;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int first_key = first_visible(pos0, a.chunk, a.window);
-  const int b_lo = first_key / kSmKeys, b_hi = last_pos / kSmKeys;
+  int b_lo = first_key / kSmKeys, b_hi = last_pos / kSmKeys;
+  if (splits > 0) {
+    const int per = (b_hi - b_lo + splits) / splits;       // tiles a share, rounded up
+    b_lo += (int)blockIdx.x * per;
+    b_hi = min(b_hi, b_lo + per - 1);                      // (an empty share writes zeros)
+  }
 
   auto fetch = [&](int stage, int b) {
     // the page of every key of the tile, once
@@ -350,7 +357,7 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       cp_async16(q_s + (size_t)r * KP + c, src, ok);
     }
   }
-  fetch(0, b_lo);
+  if (b_lo <= b_hi) fetch(0, b_lo);
 
   // this thread's two rows: g8 and g8 + 8 of the warp's sixteen
   const int g8 = lane >> 2, t4 = lane & 3;
@@ -440,6 +447,10 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     }
     __syncthreads();      // the stage is free for the fetch after next
   }
+  if (b_lo > b_hi) {      // (an empty share: the queries' copies are still in flight)
+    cp_async_commit();
+    cp_async_wait<0>();
+  }
 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -448,6 +459,16 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     const int t = r / gc, g = r - t * gc;
     const int head = kvh * group + g0 + g;
     const size_t tok = (size_t)(row0 + t0 + t);
+    if (splits > 0) {
+      float* dst = partial + (((size_t)blockIdx.x * a.q_start[gridDim.y] + tok) * a.heads + head) * vd;
+#pragma unroll
+      for (int n = 0; n < DV / 8; ++n) {
+        const int col = n * 8 + 2 * t4;
+        if (col < vd) dst[col] = o[n][2 * h];
+        if (col + 1 < vd) dst[col + 1] = o[n][2 * h + 1];
+      }
+      continue;
+    }
     float gate = 1.f;
     if (a.gate) {
       const float z = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[tok * a.ld_gate + head]
@@ -466,9 +487,29 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
 }
 
+// out[tok][head] = sigmoid(gate[tok][head]) * sum over the shares, in rising order, of partial[share][tok][head]
+__global__ void sigmoid_attention_sum_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, SigAttnArgs a,
+                                             int splits, int n_tokens) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t tok = blockIdx.x;
+  const int width = a.heads * a.vdim;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const int head = c / a.vdim;
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += partial[((size_t)s * n_tokens + tok) * width + c];
+    if (a.gate) {
+      const float z = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[tok * a.ld_gate + head]
+                                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.gate)[tok * a.ld_gate + head]);
+      v *= sig_f(z);
+    }
+    out[tok * width + c] = __float2bfloat16_rn(v);
+  }
+}
+
 template <int DK, int DV>
 static int launch_sigmoid_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const SigAttnArgs& a,
-                              int n_entries, int max_q_len, cudaStream_t stream) {
+                              int n_entries, int max_q_len, int splits, float* partial, cudaStream_t stream) {
   const size_t smem = sizeof(__nv_bfloat16) * ((size_t)kSmRows * (DK + 8) + 2 * (size_t)kSmKeys * (DK + 8) + 2 * (size_t)kSmKeys * (DV + 8));
   auto kern = sigmoid_attention_mma_kernel<DK, DV>;
   if (smem > 48 * 1024) {
@@ -480,9 +521,12 @@ static int launch_sigmoid_mma(const void* q, const void* k_pages, const void* v_
   const int q_tile = kSmRows / group_chunk;
   const int chunks = (group + group_chunk - 1) / group_chunk;
   if ((int64_t)a.kv_heads * chunks > 65535) return TIB_E_SIZE;
-  dim3 grid(ceil_div(max_q_len, q_tile), n_entries, a.kv_heads * chunks);
+  dim3 grid(splits > 0 ? splits : ceil_div(max_q_len, q_tile), n_entries, a.kv_heads * chunks);
   TIB_LAUNCH_DEPENDENT(kern, grid, kSmThreads, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
-                       (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, a, group_chunk, q_tile);
+                       (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, a, group_chunk, q_tile, splits, partial);
+  if (splits > 0)      // (a step of single tokens: one token an entry)
+    TIB_LAUNCH_DEPENDENT(sigmoid_attention_sum_kernel, n_entries, 128, 0, stream, (const float*)partial, (__nv_bfloat16*)out, a,
+                         splits, n_entries);
   return TIB_OK;
 }
 
@@ -527,15 +571,19 @@ TIB_API int tib_qk_norm_append(const void* proj, int64_t ld, int q_off, int k_of
   return TIB_OK;
 }
 
+TIB_API int tib_sigmoid_attention_takes_mma(int dim, int vdim) { return dim % 8 == 0 && vdim % 8 == 0 && dim <= 128 && vdim <= 128; }
+
 // q: [n_tokens, heads * dim]; out: [n_tokens, heads * vdim]; gate: [n_tokens, >= heads] logits (row stride ld_gate)
 // or null; head_bias: [heads] fp32 or null.  bf16 with head sizes that are multiples of 8 up to 128 runs on the tensor
-// cores unless force_simt.
+// cores unless force_simt.  splits > 0 (only there, and only when every entry brings one token): the keys of a context are
+// shared out over that many blocks, whose sums meet in partial [splits, n_entries, heads * vdim] fp32.
+
 TIB_API int tib_sigmoid_attention(const void* q, const void* k_pages, const void* v_pages, void* out, const int* q_start,
                                   const int* kv_start, const int* slots, const int* block_table, int table_stride,
                                   int n_entries, int max_q_len, int heads, int kv_heads, int dim, int vdim, int page_size,
                                   int64_t page_stride, int num_pages, int chunk, int window, float scale,
                                   const float* head_bias, const void* gate, int gate_dtype, int64_t ld_gate, int* error_word,
-                                  int dtype, int force_simt, cudaStream_t stream) {
+                                  int dtype, int force_simt, int splits, float* partial, cudaStream_t stream) {
   if (n_entries == 0 || max_q_len == 0) return TIB_OK;
   if (!q || !k_pages || !v_pages || !out || !q_start || !kv_start || !slots || !block_table) return TIB_E_ARG;
   if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || vdim < 1 || page_size < 1 || chunk < 0 || window < 0)
@@ -547,10 +595,11 @@ TIB_API int tib_sigmoid_attention(const void* q, const void* k_pages, const void
   a.num_pages = num_pages; a.chunk = chunk; a.window = window; a.scale = scale; a.head_bias = head_bias; a.gate = gate;
   a.gate_dtype = gate_dtype; a.ld_gate = ld_gate; a.error_word = error_word;
   if (dtype == TIB_BF16 && !force_simt && sigmoid_mma_takes(dim, vdim, page_stride, q, k_pages, v_pages)) {
-    if (dim <= 64 && vdim <= 64) return launch_sigmoid_mma<64, 64>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
-    if (dim <= 64) return launch_sigmoid_mma<64, 128>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
-    if (vdim <= 64) return launch_sigmoid_mma<128, 64>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
-    return launch_sigmoid_mma<128, 128>(q, k_pages, v_pages, out, a, n_entries, max_q_len, stream);
+    if (splits > 0 && (max_q_len != 1 || !partial)) return TIB_E_ARG;
+    if (dim <= 64 && vdim <= 64) return launch_sigmoid_mma<64, 64>(q, k_pages, v_pages, out, a, n_entries, max_q_len, splits, partial, stream);
+    if (dim <= 64) return launch_sigmoid_mma<64, 128>(q, k_pages, v_pages, out, a, n_entries, max_q_len, splits, partial, stream);
+    if (vdim <= 64) return launch_sigmoid_mma<128, 64>(q, k_pages, v_pages, out, a, n_entries, max_q_len, splits, partial, stream);
+    return launch_sigmoid_mma<128, 128>(q, k_pages, v_pages, out, a, n_entries, max_q_len, splits, partial, stream);
   }
   const int vpl = (vdim + 31) / 32;
 #define TIB_SA_DISPATCH(T)                                                                                   \

@@ -124,7 +124,7 @@ def lib() -> ctypes.CDLL:
                    "tib_scale_f32", "tib_pair_rows", "tib_add_vector", "tib_linear_attention", "tib_linear_attention_chunk",
                    "tib_latent_append", "tib_latent_attention", "tib_latent_attention_splits", "tib_moe_route", "tib_moe_group", "tib_router_logits",
                    "tib_moe_expert_product", "tib_moe_combine", "tib_glu_clamp", "tib_layernorm", "tib_layernorm_tail",
-                   "tib_qk_norm_append", "tib_sigmoid_attention", "tib_gated_recurrence"):
+                   "tib_qk_norm_append", "tib_sigmoid_attention", "tib_sigmoid_attention_takes_mma", "tib_gated_recurrence"):
             getattr(library, fn).restype = c_int
         _signatures_set = True
     return library
@@ -1111,11 +1111,14 @@ def sigmoid_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor,
                       kv_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, n_entries: int, max_q_len: int,
                       heads: int, kv_heads: int, *, scale: float, chunk: int = 0, window: int = 0,
                       head_bias: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-                      error_word: torch.Tensor | None = None, force_simt: bool = False) -> torch.Tensor:
+                      error_word: torch.Tensor | None = None, force_simt: bool = False, max_kv_len: int | None = None,
+                      splits: int | None = None) -> torch.Tensor:
     """out[i] = sigmoid(gate[i]) * sum over visible j of sigmoid(q_i . k_j * scale + head_bias) * v_j, per head; visible:
     j <= i, in i's chunk of ``chunk`` positions (0: no chunks) and within ``window`` (0: none).  ``gate``: [tokens, heads]
     logits (a column slice is fine) or None.  bfloat16 with head sizes that are multiples of 8 up to 128 runs on the tensor
-    cores, everything else (and ``force_simt``) on the CUDA-core kernel."""
+    cores, everything else (and ``force_simt``) on the CUDA-core kernel.  In a step of single tokens on the tensor cores the
+    keys of each context are shared out over ``splits`` blocks (None: enough to fill the GPU, from ``max_kv_len``, a bound
+    on the longest context) whose sums are added in a fixed order by a second small kernel."""
     _need(q, "q"), _need(out, "out", q.dtype)
     dim, vdim, page_size = keys.shape[3], values.shape[3], keys.shape[2]
     n = q.shape[0]
@@ -1127,13 +1130,25 @@ def sigmoid_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor,
         _need(head_bias, "head_bias", torch.float32)
     if gate is not None:
         _rows_of(gate, "gate", heads)
+    partial = None
+    if (max_q_len == 1 and q.dtype == torch.bfloat16 and not force_simt
+            and lib().tib_sigmoid_attention_takes_mma(c_int(dim), c_int(vdim))):
+        if splits is None:
+            seen = min(x for x in (chunk or None, window or None, max_kv_len, 1 << 30) if x)
+            tiles = -(-seen // 64) + 1
+            blocks = n_entries * kv_heads * -(-(heads // kv_heads) // 64)
+            splits = min(tiles, max(1, -(-2 * 148 // blocks)))
+        if splits > 1:
+            partial = torch.empty((splits, n_entries, heads * vdim), dtype=torch.float32, device=q.device)
+            count_launches(1)
+    splits = splits if partial is not None else 0
     _check("sigmoid_attention", lib().tib_sigmoid_attention(
         _ptr(q), _ptr(keys), _ptr(values), _ptr(out), _ptr(q_start), _ptr(kv_start), _ptr(slots), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(n_entries), c_int(max_q_len), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
         c_int(page_size), c_int64(keys.stride(0)), c_int(keys.shape[0]), c_int(chunk), c_int(window), c_float(scale),
         _ptr(head_bias), _ptr(gate), c_int(_code(gate.dtype) if gate is not None else 0),
         c_int64(gate.stride(0) if gate is not None else 0), _ptr(error_word), c_int(_code(q.dtype)), c_int(int(force_simt)),
-        _stream()))
+        c_int(splits), _ptr(partial), _stream()))
     return out
 
 

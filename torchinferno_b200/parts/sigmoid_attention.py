@@ -100,7 +100,8 @@ class SigmoidAttention(Mixer):
         ops.sigmoid_attention(q, kv.keys, kv.values, out, batch.q_start, batch.kv_start, batch.slots, kv.block_table,
                               batch.n_entries, batch.max_q_len, h, g, scale=self.scale, chunk=self.chunk or 0,
                               window=self.window or 0, head_bias=self.bias,
-                              gate=proj[:, self.g_off:self.g_off + h] if self.head_gate else None, error_word=ctx.error_word)
+                              gate=proj[:, self.g_off:self.g_off + h] if self.head_gate else None, error_word=ctx.error_word,
+                              max_kv_len=batch.max_kv_len)
         return linear(out, self.o_weight)
 
 
