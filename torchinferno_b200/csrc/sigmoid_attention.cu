@@ -270,7 +270,9 @@ static int launch_sigmoid_simt(const void* q, const void* k_pages, const void* v
 // of the tile are zero-filled (unwritten cache may hold anything); so are the padding columns up to DK / DV.
 constexpr int kSmRows = 64, kSmKeys = 64, kSmThreads = 128;
 
-template <int DK, int DV>
+// BYKEYS: every block of the launch has at most 16 rows (single tokens, short portions).  The four warps then share a
+// tile's keys, 16 each, instead of its rows, and their sums meet in shared memory at the end, in warp order.
+template <int DK, int DV, bool BYKEYS>
 __global__ void __launch_bounds__(kSmThreads)
 sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                              const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out, SigAttnArgs a,
@@ -364,9 +366,11 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   int qpos[2], lo[2];
   float bias[2];
   bool live[2];
+  constexpr int NT = BYKEYS ? 2 : kSmKeys / 8;      // tiles of 8 keys a warp takes of a tile of 64
+  const int row_base = BYKEYS ? 0 : warp * 16, key_base = BYKEYS ? warp * 16 : 0;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = warp * 16 + g8 + 8 * h;
+    const int r = row_base + g8 + 8 * h;
     live[h] = r < nrows;
     const int t = live[h] ? r / gc : 0, g = live[h] ? r - t * gc : 0;
     qpos[h] = pos0 + t;
@@ -389,38 +393,38 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     }
     __syncthreads();
     // (a warp whose rows see nothing of this tile still passes the barriers)
-    const int warp_first = pos0 + (warp * 16) / gc, warp_last = pos0 + min(nrows - 1, warp * 16 + 15) / gc;
-    const bool any = warp * 16 < nrows && b * kSmKeys <= warp_last &&
-                     b * kSmKeys + kSmKeys - 1 >= first_visible(warp_first, a.chunk, a.window);
+    const int warp_first = pos0 + row_base / gc, warp_last = pos0 + min(nrows - 1, row_base + 15) / gc;
+    const bool any = row_base < nrows && b * kSmKeys + key_base <= warp_last &&
+                     b * kSmKeys + key_base + NT * 8 - 1 >= first_visible(warp_first, a.chunk, a.window);
     if (any) {
       const __nv_bfloat16* kt = k_s + (size_t)stage * kSmKeys * KP;
       const __nv_bfloat16* vt = v_s + (size_t)stage * kSmKeys * VP;
-      float s[kSmKeys / 8][4];
+      float s[NT][4];
 #pragma unroll
-      for (int n = 0; n < kSmKeys / 8; ++n)
+      for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < DK; kk += 16) {
         uint32_t af[4];
-        ldmatrix_x4(af, q_s + (size_t)(warp * 16 + (lane & 15)) * KP + kk + (lane >> 4) * 8);
+        ldmatrix_x4(af, q_s + (size_t)(row_base + (lane & 15)) * KP + kk + (lane >> 4) * 8);
 #pragma unroll
-        for (int j = 0; j < kSmKeys / 16; ++j) {
+        for (int j = 0; j < NT / 2; ++j) {
           uint32_t bf[4];
-          ldmatrix_x4(bf, kt + (size_t)(j * 16 + ((lane >> 4) << 3) + (lane & 7)) * KP + kk + ((lane >> 3) & 1) * 8);
+          ldmatrix_x4(bf, kt + (size_t)(key_base + j * 16 + ((lane >> 4) << 3) + (lane & 7)) * KP + kk + ((lane >> 3) & 1) * 8);
           mma_bf16(s[2 * j], af, bf[0], bf[1]);
           mma_bf16(s[2 * j + 1], af, bf[2], bf[3]);
         }
       }
       // weights in fp32; into the second product as a high bf16 part and the remainder
-      uint32_t p_hi[kSmKeys / 16][4], p_lo[kSmKeys / 16][4];
+      uint32_t p_hi[NT / 2][4], p_lo[NT / 2][4];
 #pragma unroll
-      for (int n = 0; n < kSmKeys / 8; ++n) {
+      for (int n = 0; n < NT; ++n) {
         float w[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int h = c >> 1;
-          const int kp = b * kSmKeys + n * 8 + 2 * t4 + (c & 1);
+          const int kp = b * kSmKeys + key_base + n * 8 + 2 * t4 + (c & 1);
           const bool allowed = live[h] && kp <= qpos[h] && kp >= lo[h];
           w[c] = allowed ? __fdividef(1.f, 1.f + __expf(-(s[n][c] * a.scale + bias[h]))) : 0.f;
         }
@@ -433,11 +437,11 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
         p_lo[kk][half + 1] = pack_bf16(w[2] - f23.x, w[3] - f23.y);
       }
 #pragma unroll
-      for (int kk = 0; kk < kSmKeys / 16; ++kk) {
+      for (int kk = 0; kk < NT / 2; ++kk) {
 #pragma unroll
         for (int dn = 0; dn < DV / 16; ++dn) {
           uint32_t bv[4];
-          ldmatrix_x4_trans(bv, vt + (size_t)(kk * 16 + (lane & 15)) * VP + dn * 16 + ((lane >> 4) << 3));
+          ldmatrix_x4_trans(bv, vt + (size_t)(key_base + kk * 16 + (lane & 15)) * VP + dn * 16 + ((lane >> 4) << 3));
           mma_bf16(o[2 * dn], p_hi[kk], bv[0], bv[1]);
           mma_bf16(o[2 * dn + 1], p_hi[kk], bv[2], bv[3]);
           mma_bf16(o[2 * dn], p_lo[kk], bv[0], bv[1]);
@@ -451,11 +455,30 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     cp_async_commit();
     cp_async_wait<0>();
   }
+  if (BYKEYS) {
+    // the four warps' sums over their keys, added in warp order (the stages are free: every loop ends in a barrier)
+    float* red = reinterpret_cast<float*>(k_s);         // [4][16][DV] floats over the key and value stages, which adjoin
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        red[((size_t)warp * 16 + g8 + 8 * (c >> 1)) * DV + n * 8 + 2 * t4 + (c & 1)] = o[n][c];
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const size_t at = ((size_t)g8 + 8 * (c >> 1)) * DV + n * 8 + 2 * t4 + (c & 1);
+        o[n][c] = ((red[at] + red[16 * DV + at]) + red[32 * DV + at]) + red[48 * DV + at];
+      }
+    if (warp != 0) return;      // (warp 0 writes the rows)
+  }
 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (!live[h]) continue;
-    const int r = warp * 16 + g8 + 8 * h;
+    const int r = row_base + g8 + 8 * h;
     const int t = r / gc, g = r - t * gc;
     const int head = kvh * group + g0 + g;
     const size_t tok = (size_t)(row0 + t0 + t);
@@ -510,15 +533,17 @@ __global__ void sigmoid_attention_sum_kernel(const float* __restrict__ partial, 
 template <int DK, int DV>
 static int launch_sigmoid_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const SigAttnArgs& a,
                               int n_entries, int max_q_len, int splits, float* partial, cudaStream_t stream) {
+  static_assert(4 * 16 * DV * sizeof(float) <= 2 * kSmKeys * (DK + 8 + DV + 8) * sizeof(__nv_bfloat16), "the warps' sums fit the stages");
   const size_t smem = sizeof(__nv_bfloat16) * ((size_t)kSmRows * (DK + 8) + 2 * (size_t)kSmKeys * (DK + 8) + 2 * (size_t)kSmKeys * (DV + 8));
-  auto kern = sigmoid_attention_mma_kernel<DK, DV>;
+  const int group = a.heads / a.kv_heads;
+  const int group_chunk = group < kSmRows ? group : kSmRows;
+  const bool by_keys = (int64_t)max_q_len * group_chunk <= 16;      // no block has more than 16 rows
+  auto kern = by_keys ? sigmoid_attention_mma_kernel<DK, DV, true> : sigmoid_attention_mma_kernel<DK, DV, false>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  const int group = a.heads / a.kv_heads;
-  const int group_chunk = group < kSmRows ? group : kSmRows;
-  const int q_tile = kSmRows / group_chunk;
+  const int q_tile = by_keys ? max_q_len : kSmRows / group_chunk;
   const int chunks = (group + group_chunk - 1) / group_chunk;
   if ((int64_t)a.kv_heads * chunks > 65535) return TIB_E_SIZE;
   dim3 grid(splits > 0 ? splits : ceil_div(max_q_len, q_tile), n_entries, a.kv_heads * chunks);

@@ -1137,7 +1137,7 @@ def sigmoid_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor,
             seen = min(x for x in (chunk or None, window or None, max_kv_len, 1 << 30) if x)
             tiles = -(-seen // 64) + 1
             blocks = n_entries * kv_heads * -(-(heads // kv_heads) // 64)
-            splits = min(tiles, max(1, -(-2 * 148 // blocks)))
+            splits = min(tiles, max(1, 2 * 148 // blocks))      # (two blocks fit an SM: one wave)
         if splits > 1:
             partial = torch.empty((splits, n_entries, heads * vdim), dtype=torch.float32, device=q.device)
             count_launches(1)
