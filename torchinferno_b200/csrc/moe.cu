@@ -22,23 +22,37 @@ namespace tib {
 
 // ----------------------------------------------------------- router logits
 // out[t, e] = x[t] . w[e] in fp32 for a handful of rows w (the router, perhaps a gate row behind it): one warp per
-// (token, row), lanes stride over k, then a butterfly sum: the order of every sum is fixed by k alone, so a token's
-// logits do not depend on what else is in the step.  (The general fp32 product gives a product this narrow to a
-// single block.)
+// row and group of tokens, lanes stride over k, then a butterfly sum per token: the order of every sum is fixed by k
+// alone, so a token's logits do not depend on what else is in the step.  (The general fp32 product gives a product
+// this narrow to a single block.)
+// A block takes kRouterTokens tokens, so that a row of w read from the L2 serves several of them.
+constexpr int kRouterTokens = 4;
+
 template <typename TX>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const TX* __restrict__ x, int64_t ldx, const float* __restrict__ w, float* __restrict__ out, int64_t ldo,
-                     int rows, int K) {
+                     int tokens, int rows, int K) {
   pdl_wait();
   pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const TX* xr = x + (size_t)blockIdx.x * ldx;
+  const int t0 = blockIdx.x * kRouterTokens;
+  const int nt = min(kRouterTokens, tokens - t0);
   for (int e = warp + blockIdx.y * nwarps; e < rows; e += nwarps * gridDim.y) {
     const float* wr = w + (size_t)e * K;
-    float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(xr[k]), wr[k], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) out[(size_t)blockIdx.x * ldo + e] = acc;
+    float acc[kRouterTokens];
+#pragma unroll
+    for (int i = 0; i < kRouterTokens; ++i) acc[i] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float wv = wr[k];
+#pragma unroll
+      for (int i = 0; i < kRouterTokens; ++i)
+        if (i < nt) acc[i] = fmaf(to_f32(x[(size_t)(t0 + i) * ldx + k]), wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < kRouterTokens; ++i) {
+      const float v = warp_sum(acc[i]);
+      if (lane == 0 && i < nt) out[(size_t)(t0 + i) * ldo + e] = v;
+    }
   }
 }
 
@@ -355,12 +369,13 @@ TIB_API int tib_router_logits(const void* x, int x_dtype, int64_t ldx, const flo
   if (!x || !w || !out || tokens < 0 || rows < 0 || K < 1) return TIB_E_ARG;
   if (tokens > 0x7fffffff / 2) return TIB_E_SIZE;
   int slices = 1;      // few tokens: the rows of w are spread over several blocks a token
-  while (tokens * slices < 2 * 148 && slices * 8 < rows) slices *= 2;
-  dim3 grid(tokens, slices);
+  const int groups = ceil_div(tokens, kRouterTokens);
+  while (groups * slices < 2 * 148 && slices * 8 < rows) slices *= 2;
+  dim3 grid(groups, slices);
   if (x_dtype == TIB_F32)
-    TIB_LAUNCH_DEPENDENT(router_logits_kernel<float>, grid, 256, 0, stream, (const float*)x, ldx, w, out, ldo, rows, K);
+    TIB_LAUNCH_DEPENDENT(router_logits_kernel<float>, grid, 256, 0, stream, (const float*)x, ldx, w, out, ldo, tokens, rows, K);
   else if (x_dtype == TIB_BF16)
-    TIB_LAUNCH_DEPENDENT(router_logits_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)x, ldx, w, out, ldo, rows, K);
+    TIB_LAUNCH_DEPENDENT(router_logits_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)x, ldx, w, out, ldo, tokens, rows, K);
   else
     return TIB_E_DTYPE;
   return TIB_OK;

@@ -38,7 +38,7 @@ struct QkAppendArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 qk_norm_append_kernel(const T* __restrict__ proj, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                       QkAppendArgs a) {
   pdl_wait();
@@ -517,9 +517,10 @@ __global__ void sigmoid_attention_sum_kernel(const float* __restrict__ partial, 
   pdl_trigger();
   const size_t tok = blockIdx.x;
   const int width = a.heads * a.vdim;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
     const int head = c / a.vdim;
     float v = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) v += partial[((size_t)s * n_tokens + tok) * width + c];
     if (a.gate) {
       const float z = a.gate_dtype == TIB_F32 ? reinterpret_cast<const float*>(a.gate)[tok * a.ld_gate + head]
@@ -550,8 +551,8 @@ static int launch_sigmoid_mma(const void* q, const void* k_pages, const void* v_
   TIB_LAUNCH_DEPENDENT(kern, grid, kSmThreads, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,
                        (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, a, group_chunk, q_tile, splits, partial);
   if (splits > 0)      // (a step of single tokens: one token an entry)
-    TIB_LAUNCH_DEPENDENT(sigmoid_attention_sum_kernel, n_entries, 128, 0, stream, (const float*)partial, (__nv_bfloat16*)out, a,
-                         splits, n_entries);
+    TIB_LAUNCH_DEPENDENT(sigmoid_attention_sum_kernel, dim3(n_entries, ceil_div(a.heads * a.vdim, 128)), 128, 0, stream,
+                         (const float*)partial, (__nv_bfloat16*)out, a, splits, n_entries);
   return TIB_OK;
 }
 
@@ -582,7 +583,8 @@ TIB_API int tib_qk_norm_append(const void* proj, int64_t ld, int q_off, int k_of
   a.vdim = vdim; a.rot_dim = rot_dim; a.interleaved = interleaved; a.eps = eps; a.positions = positions;
   a.token_slot = token_slot; a.block_table = block_table; a.table_stride = table_stride; a.inv_freq = inv_freq;
   a.page_size = page_size; a.page_stride = page_stride; a.num_pages = num_pages; a.error_word = error_word;
-  const int threads = 128;
+  const int rot_heads = heads + (k_off >= 0 ? kv_heads : 0);
+  const int threads = 32 * (rot_heads < 4 ? 4 : rot_heads > 16 ? 16 : rot_heads);      // a warp a head, up to sixteen
   const size_t smem = sizeof(float) * ((size_t)rot_dim + (size_t)(threads / 32) * dim);
   if (smem > 48 * 1024) return TIB_E_SIZE;
   if (dtype == TIB_F32)
