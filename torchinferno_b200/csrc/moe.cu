@@ -347,7 +347,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   pdl_trigger();
   const size_t t = blockIdx.x;
   const float g = (shared && gate) ? 1.f / (1.f + expf(-gate[t * ld_gate])) : 1.f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
     float v = 0.f;
     for (int k = 0; k < top; ++k) {
       const int s = place[t * top + k];
@@ -442,8 +442,10 @@ TIB_API int tib_moe_combine(const float* y, const int* place, const float* weigh
   if (tokens == 0 || width == 0) return TIB_OK;
   if (!y || !place || !out || top < 1) return TIB_E_ARG;
   const int threads = width >= 1024 ? 256 : 128;
+  // (few tokens: a row's columns are spread over several blocks)
+  const dim3 grid(tokens, tokens < 2 * 148 ? ceil_div(width, threads) : 1);
 #define TIB_COMBINE_GO(TS, TO)                                                                                       \
-  TIB_LAUNCH_DEPENDENT((moe_combine_kernel<TS, TO>), tokens, threads, 0, stream, y, place, weights, top, (const TS*)shared, gate, \
+  TIB_LAUNCH_DEPENDENT((moe_combine_kernel<TS, TO>), grid, threads, 0, stream, y, place, weights, top, (const TS*)shared, gate, \
                        ld_gate, (TO*)out, width)
   const int sd = shared ? shared_dtype : out_dtype;
   if (sd == TIB_F32 && out_dtype == TIB_F32) TIB_COMBINE_GO(float, float);
