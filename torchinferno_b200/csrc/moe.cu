@@ -22,13 +22,26 @@ namespace tib {
 
 // ----------------------------------------------------------- router logits
 // out[t, e] = x[t] . w[e] in fp32 for a handful of rows w (the router, perhaps a gate row behind it): one warp per
-// row and group of tokens, lanes stride over k, then a butterfly sum per token: the order of every sum is fixed by k
-// alone, so a token's logits do not depend on what else is in the step.  (The general fp32 product gives a product
+// row and group of tokens, lanes stride over k (eight at a time where rows are 16-byte aligned), then a butterfly sum per
+// token: the order of every sum is fixed by k and the alignment alone, so a token's logits do not depend on what else is
+// in the step.  (The general fp32 product gives a product
 // this narrow to a single block.)
-// A block takes kRouterTokens tokens, so that a row of w read from the L2 serves several of them.
+// A block takes kRouterTokens tokens, so that a row of w read from the L2 serves several of them.  With 16-byte aligned
+// rows (VEC) a lane takes eight consecutive k at a time: 16 bytes of a bf16 token row, 32 bytes of w.
 constexpr int kRouterTokens = 4;
 
-template <typename TX>
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const float2 a = bf16x2_floats(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), b = bf16x2_floats(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  const float2 c = bf16x2_floats(*reinterpret_cast<const __nv_bfloat162*>(&raw.z)), d = bf16x2_floats(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+
+template <typename TX, bool VEC>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const TX* __restrict__ x, int64_t ldx, const float* __restrict__ w, float* __restrict__ out, int64_t ldo,
                      int tokens, int rows, int K) {
@@ -37,12 +50,27 @@ router_logits_kernel(const TX* __restrict__ x, int64_t ldx, const float* __restr
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int t0 = blockIdx.x * kRouterTokens;
   const int nt = min(kRouterTokens, tokens - t0);
+  const int K8 = VEC ? (K / 8) * 8 : 0;
   for (int e = warp + blockIdx.y * nwarps; e < rows; e += nwarps * gridDim.y) {
     const float* wr = w + (size_t)e * K;
     float acc[kRouterTokens];
 #pragma unroll
     for (int i = 0; i < kRouterTokens; ++i) acc[i] = 0.f;
-    for (int k = lane; k < K; k += 32) {
+    if (VEC) {
+      for (int k = lane * 8; k < K8; k += 256) {
+        float wv[8];
+        load8(wr + k, wv);
+#pragma unroll
+        for (int i = 0; i < kRouterTokens; ++i) {
+          if (i >= nt) continue;
+          float xv[8];
+          load8(x + (size_t)(t0 + i) * ldx + k, xv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i] = fmaf(xv[j], wv[j], acc[i]);
+        }
+      }
+    }
+    for (int k = K8 + lane; k < K; k += 32) {
       const float wv = wr[k];
 #pragma unroll
       for (int i = 0; i < kRouterTokens; ++i)
@@ -372,10 +400,13 @@ TIB_API int tib_router_logits(const void* x, int x_dtype, int64_t ldx, const flo
   const int groups = ceil_div(tokens, kRouterTokens);
   while (groups * slices < 2 * 148 && slices * 8 < rows) slices *= 2;
   dim3 grid(groups, slices);
-  if (x_dtype == TIB_F32)
-    TIB_LAUNCH_DEPENDENT(router_logits_kernel<float>, grid, 256, 0, stream, (const float*)x, ldx, w, out, ldo, tokens, rows, K);
-  else if (x_dtype == TIB_BF16)
-    TIB_LAUNCH_DEPENDENT(router_logits_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)x, ldx, w, out, ldo, tokens, rows, K);
+  const int64_t xbytes = x_dtype == TIB_F32 ? 4 : 2;
+  const bool vec = K % 4 == 0 && (ldx * xbytes) % 16 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0;
+#define TIB_ROUTER_GO(TX, VEC) \
+  TIB_LAUNCH_DEPENDENT((router_logits_kernel<TX, VEC>), grid, 256, 0, stream, (const TX*)x, ldx, w, out, ldo, tokens, rows, K)
+  if (x_dtype == TIB_F32) { if (vec) TIB_ROUTER_GO(float, true); else TIB_ROUTER_GO(float, false); }
+  else if (x_dtype == TIB_BF16) { if (vec) TIB_ROUTER_GO(__nv_bfloat16, true); else TIB_ROUTER_GO(__nv_bfloat16, false); }
+#undef TIB_ROUTER_GO
   else
     return TIB_E_DTYPE;
   return TIB_OK;
