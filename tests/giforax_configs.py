@@ -62,4 +62,13 @@ GD = {
         layer("attention", attention(6, 1, 40, 16, 33, 0.15, 20, kv_from=0), None),
     ],
 }
-CONFIGS = {"GA": (GA, 21), "GB": (GB, 22), "GC": (GC, 23), "GD": (GD, 24)}
+# nothing is a multiple of 4: width 50, heads of 6 and 10, a recurrence of 7 channels, experts of 9, a vocabulary of 53
+GE = {
+    "architecture": "Giforax", "vocab": 53, "width": 50, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+    "layers": [
+        layer("attention", attention(3, 3, 6, 10, 9, 0.4, 2), moe(3, 2, 9, 1.0, shared=5)),
+        layer("mingru", {"width": 7}, moe(2, 1, 3, 2.0)),
+        layer("attention", attention(6, 3, 6, 10, 21, 0.4, 2, kv_from=0), None),
+    ],
+}
+CONFIGS = {"GA": (GA, 21), "GB": (GB, 22), "GC": (GC, 23), "GD": (GD, 24), "GE": (GE, 25)}

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_giforax
-from giforax_configs import CONFIGS, GA, GB, GC, GD
+from giforax_configs import CONFIGS, GA, GB, GC, GD, GE
 
 
 def test_the_registry_resolves_the_design():
@@ -20,7 +20,7 @@ def test_the_registry_resolves_the_design():
 def test_config_errors_name_what_is_missing_or_wrong():
     from torchinferno_b200.config.giforax_config import GiforaxConfig
     from torchinferno_b200.config.model_config import ConfigError
-    for config in (GA, GB, GC, GD):
+    for config in (GA, GB, GC, GD, GE):
         GiforaxConfig.from_dict(config)
     for path, value in ((("width",), None), (("embedding",), None), (("norm", "eps"), 0.0), (("layers", 0, "type"), "conv"),
                         (("layers", 0, "mixer", "rot", "dims"), 7), (("layers", 0, "mixer", "rot", "dims"), 18),

@@ -131,7 +131,7 @@ def test_whole_tail_portions_and_mixed_batches(name, dtype, folders):
     need_gpu()
     config, seed = CONFIGS[name]
     requests = requests_for(config, seed, [1, 2, 37, 70, 131, 64, 33])
-    page = {"GA": 16, "GB": 4, "GC": 8, "GD": 8}[name]
+    page = {"GA": 16, "GB": 4, "GC": 8, "GD": 8, "GE": 2}[name]
     for kind, (steps, index) in {
             "whole": replay_util.trace_whole(requests), "tail": replay_util.trace_tail_decode(requests, tail=40),
             "portions": replay_util.trace_portions(requests, sizes=(2, 7, 16, 3, 33, 2, 5, 31, 32, 2, 64)),
@@ -425,7 +425,7 @@ def test_routed_gated_units_alone(dtype, experts, top, shared, tokens):
         assert len(set(torch.sigmoid(x.double() @ w["mlp.router"].T).argmax(-1).tolist())) > 1
 
 
-@pytest.mark.parametrize("width,rows", [(44, 7), (192, 300), (4096, 5)])
+@pytest.mark.parametrize("width,rows", [(44, 7), (50, 9), (192, 300), (4096, 5), (9000, 3)])
 def test_layer_norm_and_the_tails_of_sublayers(width, rows):
     """The norm alone (gathered rows too), and the fused tail: norm of a sublayer's output, sum into the residual, the
     average over the layers so far, the norm that opens what follows.  Rows with a large mean, where a one-pass variance
