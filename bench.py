@@ -418,12 +418,22 @@ def run_ours(args) -> dict:
 DESIGN_WIDTH, DESIGN_HEADS, DESIGN_VOCAB, DESIGN_LAYERS = 2048, 16, 32000, 4
 
 
-def design_configs() -> dict:
+def design_configs(width: int = DESIGN_WIDTH) -> dict:
+    """The designs' configurations at ``width``: heads of 128 (width / 128 of them, half as many key heads), feed-forwards of
+    four times the width, experts of half the width.  The default is what the figures in the documents were taken at."""
+    if width == DESIGN_WIDTH:
+        return _design_configs(DESIGN_WIDTH, DESIGN_HEADS, 8, 8192, 1024, 2048)
+    if width % 256 or width < 256:
+        raise ValueError("a design width is a multiple of 256")
+    return _design_configs(width, width // 128, width // 256, 4 * width, width // 2, width)
+
+
+def _design_configs(DESIGN_WIDTH: int, DESIGN_HEADS: int, kv_heads: int, dense_ff: int, expert_ff: int, shared_ff: int) -> dict:
     latent = {"heads": DESIGN_HEADS, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
               "rot": {"base": 500000.0, "dims": 64}}
     lightning = {"heads": DESIGN_HEADS, "dim": 128, "vdim": 128, "decay": [1 - 2.0 ** -(3 + i % 6) for i in range(DESIGN_HEADS)]}
-    dense = {"kind": "dense", "ff": 8192}
-    routed = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": 1024}, "shared": {"ff": 2048}}
+    dense = {"kind": "dense", "ff": dense_ff}
+    routed = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
     # (a loop of one pass: four layer runs, as the Llama beside it has, with the pass's input product once)
     zipedra = {"architecture": "Zipedra", "vocab": DESIGN_VOCAB, "width": DESIGN_WIDTH, "logit_scale": 1.0, "norm": {"eps": 1e-6},
                "token_side": {"dim": 64}, "loop": {"start": 1, "stop": 3, "times": 1},
@@ -432,14 +442,15 @@ def design_configs() -> dict:
                           {"type": "latent_attention", "mixer": latent, "mlp": routed},
                           {"type": "lightning", "mixer": lightning, "mlp": dense}]}
     llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": DESIGN_VOCAB, "hidden_size": DESIGN_WIDTH,
-             "intermediate_size": 8192, "num_hidden_layers": DESIGN_LAYERS, "num_attention_heads": DESIGN_HEADS,
-             "num_key_value_heads": 8, "head_dim": 128, "max_position_embeddings": 8192, "rope_theta": 500000.0,
+             "intermediate_size": dense_ff, "num_hidden_layers": DESIGN_LAYERS, "num_attention_heads": DESIGN_HEADS,
+             "num_key_value_heads": kv_heads, "head_dim": 128, "max_position_embeddings": 8192, "rope_theta": 500000.0,
              "rope_scaling": None, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
     # Giforax beside the same Llama: the same head counts and head size in chunks of 512 positions, a second attention
     # layer that reads the first one's keys, a recurrence as wide as the model, routed experts of the same sizes
-    sigmoid = {"heads": DESIGN_HEADS, "kv_heads": 8, "dim": 128, "vdim": 128, "mask": {"size": 512}, "scale": 0.09,
+    sigmoid = {"heads": DESIGN_HEADS, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "mask": {"size": 512}, "scale": 0.09,
                "rot": {"base": 500000.0, "dims": 64}}
-    gated = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": 1024, "limit": 7.0}, "shared": {"ff": 2048, "limit": 7.0}}
+    gated = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": expert_ff, "limit": 7.0},
+             "shared": {"ff": shared_ff, "limit": 7.0}}
     giforax = {"architecture": "Giforax", "vocab": DESIGN_VOCAB, "width": DESIGN_WIDTH, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
                "layers": [{"type": "attention", "mixer": sigmoid, "mlp": gated},
                           {"type": "attention", "mixer": dict(sigmoid, kv_from=0), "mlp": gated},
@@ -462,7 +473,7 @@ def run_design(args) -> dict:
     prompt_len, batch, steps = 2048, args.batch, min(args.steps, 64)
     points = {}
     with torch.inference_mode():
-        for name, config in design_configs().items():
+        for name, config in design_configs(args.design_width).items():
             if name not in (args.design, "llama"):
                 continue
             model = random_model(config, seed=0, dtype="bfloat16")
@@ -505,12 +516,13 @@ def run_design(args) -> dict:
             own = {"zipedra": (["latent-attention"], ["linear-attention"], ["expert-product"]),
                    "giforax": (["sigmoid-attention"], ["sigmoid-attention", "--chunk", "2048"], ["gated-recurrence"], ["layer-tails"],
                                ["expert-product"])}[args.design]
-            for argv in (*own, ["prefill-attention", "--heads", "16", "--kv-heads", "8"],
-                         ["decode-attention", "--heads", "16", "--kv-heads", "8"]):
+            alone = () if args.design_no_kernels else (*own, ["prefill-attention", "--heads", "16", "--kv-heads", "8"],
+                                                       ["decode-attention", "--heads", "16", "--kv-heads", "8"])
+            for argv in alone:
                 bench_kernels.main(argv)
     kernels = [json.loads(line) for line in lines.getvalue().splitlines() if line.startswith("{")]
     return {"design": args.design, "beside": "llama", "dtype": "bf16", "data": "synthetic token ids, random weights",
-            "config": {"width": DESIGN_WIDTH, "heads": DESIGN_HEADS, "layer_runs": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
+            "config": {"width": args.design_width, "heads": args.design_width // 128, "layer_runs": DESIGN_LAYERS, "vocab": DESIGN_VOCAB,
                        "prompt_len": prompt_len, "batch": batch, "decode_steps": steps, "page_size": PAGE_SIZE},
             "points": points, "kernels": kernels}
 
@@ -614,6 +626,9 @@ def main(argv=None) -> int:
     parser.add_argument("--design", choices=["zipedra", "giforax"], default=None,
                         help="instead of the headline run: prefill and decode throughput of this design at layer sizes that "
                              "resemble a real model's, beside the closest Llama, and its kernels against the roofline")
+    parser.add_argument("--design-width", type=int, default=DESIGN_WIDTH,
+                        help="with --design: the model width (a multiple of 256; heads of 128, the other sizes in proportion)")
+    parser.add_argument("--design-no-kernels", action="store_true", help="with --design: the step figures only")
     args = parser.parse_args(argv)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
