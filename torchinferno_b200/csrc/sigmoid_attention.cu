@@ -286,7 +286,8 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(sm_raw);          // [64][KP]
   __nv_bfloat16* k_s = q_s + kSmRows * KP;                                 // [2][64][KP]
   __nv_bfloat16* v_s = k_s + 2 * kSmKeys * KP;                             // [2][64][VP]
-  __shared__ int key_page[2][kSmKeys];
+  __shared__ long long page_base[2][kSmKeys];
+  __shared__ int key_row[2][kSmKeys];
 
   const int d = a.dim, vd = a.vdim;
   const int entry = blockIdx.y;
@@ -314,36 +315,37 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
 
   auto fetch = [&](int stage, int b) {
-    // the page of every key of the tile, once
+    // where every key of the tile lives, once: its page's first element and its row in the page
     if (tid < kSmKeys) {
       const int kp = b * kSmKeys + tid;
-      int page = -1;
+      long long base = -1;
+      int row = 0;
       if (kp <= last_pos && kp >= first_key) {
-        page = table[kp / a.page_size];
+        const int logical = kp / a.page_size;
+        const int page = table[logical];
         if (page < 0 || page >= a.num_pages) {
           if (a.error_word) atomicExch(a.error_word, 0x10000 + entry);
-          page = -1;
+        } else {
+          base = (long long)page * a.page_stride;
+          row = kvh * a.page_size + (kp - logical * a.page_size);
         }
       }
-      key_page[stage][tid] = page;
+      page_base[stage][tid] = base;
+      key_row[stage][tid] = row;
     }
     __syncthreads();
     constexpr int KPIECES = DK / 8, VPIECES = DV / 8;
     for (int e = tid; e < kSmKeys * KPIECES; e += kSmThreads) {
       const int j = e / KPIECES, c = (e - j * KPIECES) * 8;
-      const int page = key_page[stage][j];
-      const bool ok = page >= 0 && c < d;
-      const int kp = b * kSmKeys + j;
-      const __nv_bfloat16* src = k_pages + (size_t)max(page, 0) * a.page_stride + ((size_t)kvh * a.page_size + (kp % a.page_size)) * d + (ok ? c : 0);
-      cp_async16(k_s + ((size_t)stage * kSmKeys + j) * KP + c, src, ok);
+      const long long base = page_base[stage][j];
+      const bool ok = base >= 0 && c < d;
+      cp_async16(k_s + ((size_t)stage * kSmKeys + j) * KP + c, k_pages + (ok ? base + (long long)key_row[stage][j] * d + c : 0), ok);
     }
     for (int e = tid; e < kSmKeys * VPIECES; e += kSmThreads) {
       const int j = e / VPIECES, c = (e - j * VPIECES) * 8;
-      const int page = key_page[stage][j];
-      const bool ok = page >= 0 && c < vd;
-      const int kp = b * kSmKeys + j;
-      const __nv_bfloat16* src = v_pages + (size_t)max(page, 0) * a.page_stride + ((size_t)kvh * a.page_size + (kp % a.page_size)) * vd + (ok ? c : 0);
-      cp_async16(v_s + ((size_t)stage * kSmKeys + j) * VP + c, src, ok);
+      const long long base = page_base[stage][j];
+      const bool ok = base >= 0 && c < vd;
+      cp_async16(v_s + ((size_t)stage * kSmKeys + j) * VP + c, v_pages + (ok ? base + (long long)key_row[stage][j] * vd + c : 0), ok);
     }
     cp_async_commit();
   };
@@ -438,14 +440,18 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       }
 #pragma unroll
       for (int kk = 0; kk < NT / 2; ++kk) {
+        // (the two terms of the weights go in two passes, so that products into one accumulator are not back to back)
+        uint32_t bv[DV / 16][4];
 #pragma unroll
         for (int dn = 0; dn < DV / 16; ++dn) {
-          uint32_t bv[4];
-          ldmatrix_x4_trans(bv, vt + (size_t)(key_base + kk * 16 + (lane & 15)) * VP + dn * 16 + ((lane >> 4) << 3));
-          mma_bf16(o[2 * dn], p_hi[kk], bv[0], bv[1]);
-          mma_bf16(o[2 * dn + 1], p_hi[kk], bv[2], bv[3]);
-          mma_bf16(o[2 * dn], p_lo[kk], bv[0], bv[1]);
-          mma_bf16(o[2 * dn + 1], p_lo[kk], bv[2], bv[3]);
+          ldmatrix_x4_trans(bv[dn], vt + (size_t)(key_base + kk * 16 + (lane & 15)) * VP + dn * 16 + ((lane >> 4) << 3));
+          mma_bf16(o[2 * dn], p_hi[kk], bv[dn][0], bv[dn][1]);
+          mma_bf16(o[2 * dn + 1], p_hi[kk], bv[dn][2], bv[dn][3]);
+        }
+#pragma unroll
+        for (int dn = 0; dn < DV / 16; ++dn) {
+          mma_bf16(o[2 * dn], p_lo[kk], bv[dn][0], bv[dn][1]);
+          mma_bf16(o[2 * dn + 1], p_lo[kk], bv[dn][2], bv[dn][3]);
         }
       }
     }
